@@ -15,7 +15,8 @@ Beyond the reference (which has one group and no state):
   tables of its own.  A page id is valid for every layer of its group.
 * **Windows.** In a group with ``window`` W > 0 a query at position p reads keys
   p-W+1..p only, so once a request's committed length is n every page that lies wholly
-  below n-W+1 is given back at once and its table entry becomes -1.
+  below n-W+1 is given back at once and its table entry becomes -1.  With ``keep_first`` F > 0
+  the keys 0..F-1 stay readable too, and the pages that hold them stay with the request.
 * **State slots.** Every admitted request holds one slot id; mixers with per-request
   state of fixed size index their state tensors with it.  A slot is marked dirty at
   admission so that the device side zeroes the state before the request's first step.
@@ -110,11 +111,14 @@ class PageAllocator:
 @dataclass(frozen=True)
 class GroupSpec:
     """One group of layers: ``window`` 0 keeps all keys; ``bytes_per_token`` is what one
-    token costs over all layers of the group (used only to split a byte budget)."""
+    token costs over all layers of the group (used only to split a byte budget).  ``keep_first``:
+    a windowed group whose queries also read the request's first so many tokens for ever; the
+    pages that hold them are never given back behind the window."""
 
     name: str
     window: int = 0
     bytes_per_token: int = 0
+    keep_first: int = 0
 
 
 class _Group:
@@ -256,12 +260,15 @@ class CacheManager:
             table = group.tables[request_id]
             # the next query sits at position `length`; it reads keys >= length - window + 1
             keep_from = group.first_needed_page(length)
-            retired = [table[i] for i in range(min(keep_from, len(table))) if table[i] != NO_PAGE]
+            # pages that hold a token the window keeps for ever stay
+            pinned = -(-group.spec.keep_first // group.allocator.page_size) if group.spec.keep_first > 0 else 0
+            span = range(pinned, min(keep_from, len(table)))
+            retired = [table[i] for i in span if table[i] != NO_PAGE]
             if retired:
                 group.allocator.free(retired, request_id)
-                for index in range(min(keep_from, len(table))):
+                for index in span:
                     table[index] = NO_PAGE
-                group.host_table[slot, :keep_from] = NO_PAGE
+                group.host_table[slot, pinned:keep_from] = NO_PAGE
 
     # ------------------------------------------------------------ queries
     def committed_length(self, request_id: Hashable) -> int:

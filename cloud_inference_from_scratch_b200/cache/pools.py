@@ -35,11 +35,14 @@ def plan_groups(needs: list[Any], element_size: int) -> tuple[list[GroupSpec], d
     for index, key in enumerate(keys):
         window, kv_heads, head_dim = key[:3]
         value_dim = key[3] if len(key) > 3 else head_dim
+        keep_first = key[4] if len(key) > 4 else 0
         entries = members[key]
         groups.append(
             GroupSpec(
-                name=f"window{window}" if window else "full" + (f"-{index}" if index else ""),
+                name=(f"window{window}" + (f"+{keep_first}" if keep_first else "")) if window
+                else "full" + (f"-{index}" if index else ""),
                 window=window,
+                keep_first=keep_first,
                 bytes_per_token=kv_heads * (head_dim + value_dim) * element_size * len(entries),
             )
         )
@@ -75,7 +78,8 @@ def plan_page_counts(groups: list[GroupSpec], page_size: int, max_requests: int,
     caps: list[int | None] = []
     for group in groups:
         if group.window > 0 and step_tokens > 0:
-            caps.append(max_requests * (-(-(group.window + step_tokens) // page_size) + 1))
+            caps.append(max_requests * (-(-(group.window + step_tokens) // page_size) + 1
+                                        + -(-group.keep_first // page_size)))
         else:
             caps.append(None)
 

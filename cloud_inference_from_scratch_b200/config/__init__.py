@@ -8,13 +8,14 @@ from .registry import (
     resolve_config,
     resolve_model,
 )
+from .lazilorn_config import LazilornConfig
 from .lodalix_config import LodalixConfig
 from .zisesun_config import ZisesunConfig
 from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
 __all__ = [
     "Architecture", "ConfigError", "EngineConfig", "LayerSpec", "ModelSpec", "PartSpec",
-    "LodalixConfig", "Qwen2Config", "ScheduleEntry", "ZisesunConfig", "architecture_for", "build_config", "read_config_json",
+    "LazilornConfig", "LodalixConfig", "Qwen2Config", "ScheduleEntry", "ZisesunConfig", "architecture_for", "build_config", "read_config_json",
     "register_architecture", "registered_architectures", "resolve_config", "resolve_model",
     "validate_config", "with_overrides",
 ]

@@ -87,10 +87,14 @@ class ScheduleEntry:
     ``reads_cache_of``  index of an EARLIER schedule entry whose cache (pages and
                    per-request state) this run reads instead of owning one; then it
                    writes nothing to a cache.
+    ``entry_offset``  (tensor name, row): row ``row`` of the stored tensor [rows, hidden] is
+                   added to the residual stream of every token right before this run (a
+                   learned offset per pass of a looped run of layers).
     """
 
     layer: int
     reads_cache_of: int | None = None
+    entry_offset: tuple[str, int] | None = None
 
 
 @dataclass(frozen=True)
@@ -116,6 +120,11 @@ class ModelSpec:
     # copies of the residual stream that the blocks keep side by side (hyper-connections); all start
     # as the embedding rows and their sum is what the final norm reads
     residual_streams: int = 1
+    # a sinusoid of the position added to the embedding rows: entry 2i gets sin(p * base^(-2i / hidden)),
+    # entry 2i + 1 the cosine of the same angle (None: none)
+    position_wave_base: float | None = None
+    # rows of each tensor that a schedule entry names as its ``entry_offset``
+    offset_tensors: tuple[tuple[str, int], ...] = ()
 
     def validate(self) -> None:
         if not self.layers:
@@ -124,6 +133,16 @@ class ModelSpec:
             raise ValueError("logit_softcap must be >= 0")
         if self.residual_streams < 1:
             raise ValueError("residual_streams must be >= 1")
+        if self.position_wave_base is not None and not self.position_wave_base > 0:
+            raise ValueError("position_wave_base must be positive")
+        rows_of = dict(self.offset_tensors)
+        for index, entry in enumerate(self.schedule):
+            if entry.entry_offset is not None:
+                name, row = entry.entry_offset
+                if name not in rows_of or not 0 <= row < rows_of[name]:
+                    raise ValueError(f"schedule entry {index} adds row {row} of {name!r}, which offset_tensors does not have")
+                if self.residual_streams != 1:
+                    raise ValueError("entry offsets are built for one residual stream")
         for index, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule entry {index} names layer {entry.layer}, which does not exist")

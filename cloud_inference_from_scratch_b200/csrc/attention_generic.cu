@@ -12,6 +12,10 @@
 // Two generalisations (cie_attention_generic_ex): value heads of a size of their own (`vdim`), and
 // a logarithmic distance penalty per query head, s = (q.k) * scale - r1[h] * log(1 + r2[h] * (p - j))
 // for a key at position j (r1 == nullptr: none).
+//
+// `keep_first` > 0 (with a window): the first keep_first keys of the request stay visible after the
+// window has moved past them; the visible keys are then 0..keep_first-1 and p-window+1..p, visited in
+// that order as one list.
 #include "common.cuh"
 
 #include <cfloat>
@@ -30,7 +34,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ positions, const int* __restrict__ request_of_token,
                          const int* __restrict__ table, int table_width, int num_pages, int tokens,
                          int q_heads, int kv_heads, int dim, int vdim, int page_size, float scale, int window,
-                         const float* __restrict__ r1, const float* __restrict__ r2, int* err) {
+                         int keep_first, const float* __restrict__ r1, const float* __restrict__ r2, int* err) {
   __shared__ float q_s[kWarps][kMaxDim];
   __shared__ float p_s[kWarps][32];
   __shared__ long long off_s[kWarps][32];
@@ -45,7 +49,11 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
   const int request = request_of_token[t];
   const int* row = table + (size_t)request * table_width;
   const int length = pos + 1;
-  const int first = (window > 0 && length > window) ? length - window : 0;
+  int first = (window > 0 && length > window) ? length - window : 0;
+  int kept = 0;                       // keys before the window that stay visible
+  if (first > keep_first) kept = keep_first;
+  else first = 0;
+  const int visible = kept + length - first;
   const float penalty = r1 ? r1[h] : 0.f, reach = r1 ? r2[h] : 0.f;
 
   const T* qv = q + (size_t)t * q_stride + (size_t)h * dim;
@@ -57,9 +65,10 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
 #pragma unroll
   for (int i = 0; i < kMaxDim / 32; ++i) acc[i] = 0.f;
 
-  for (int base = first; base < length; base += 32) {
-    const int key = base + lane;
-    const bool valid = key < length;
+  for (int base = 0; base < visible; base += 32) {
+    const int seen = base + lane;
+    const bool valid = seen < visible;
+    const int key = seen < kept ? seen : first + (seen - kept);
     long long offset = -1;
     if (valid) {
       const int index = key / page_size;
@@ -88,7 +97,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     __syncwarp();
 #pragma unroll
     for (int i = 0; i < kMaxDim / 32; ++i) acc[i] *= alpha;
-    const int count = min(32, length - base);
+    const int count = min(32, visible - base);
     for (int j = 0; j < count; ++j) {
       const long long o = off_s[warp][j];
       if (o < 0) continue;
@@ -142,7 +151,7 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                        const int* __restrict__ positions, const int* __restrict__ request_of_token,
                        const int* __restrict__ table, int table_width, int num_pages, int q_heads,
-                       int kv_heads, int dim, int vdim, int page_size, float scale, int window,
+                       int kv_heads, int dim, int vdim, int page_size, float scale, int window, int keep_first,
                        const float* __restrict__ r1, const float* __restrict__ r2, int splits,
                        float* __restrict__ shares, int* __restrict__ tickets, int* err) {
   // splits > 1: the keys of a token are cut into that many ranges, one CTA each (blockIdx.x = token *
@@ -167,10 +176,14 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
   const int pos = positions[t];
   const int* row = table + (size_t)request_of_token[t] * table_width;
   const int length = pos + 1;
-  const int first = (window > 0 && length > window) ? length - window : 0;
-  // this CTA's keys: whole blocks of 32, counted from the first visible key
-  const int per = ((length - first + splits - 1) / splits + 31) / 32 * 32;
-  const int my_first = first + split * per, my_end = min(length, my_first + per);
+  int first = (window > 0 && length > window) ? length - window : 0;
+  int kept = 0;                       // keys before the window that stay visible
+  if (first > keep_first) kept = keep_first;
+  else first = 0;
+  const int visible = kept + length - first;
+  // this CTA's keys: whole blocks of 32 of the list of visible keys
+  const int per = ((visible + splits - 1) / splits + 31) / 32 * 32;
+  const int my_first = split * per, my_end = min(visible, my_first + per);
   for (int e = threadIdx.x; e < kGroupHeads * dim; e += blockDim.x) {
     const int h = e / dim, d = e % dim;
     q_s[e] = h < heads ? to_float(q[(size_t)t * q_stride + (size_t)(kvh * group + h0 + h) * dim + d]) : 0.f;
@@ -193,9 +206,10 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
   float* my_p = p_s + warp * kGroupHeads * 32;
   long long* my_slot = slot_s + warp * 32;
   for (int base = my_first + warp * 32; base < my_end; base += kGroupWarps * 32) {
-    const int key = base + lane;
+    const int seen = base + lane;
+    const int key = seen < kept ? seen : first + (seen - kept);
     long long slot = -1;
-    if (key < my_end) {
+    if (seen < my_end) {
       const int index = key / page_size;
       const int page = index < table_width ? row[index] : -1;
       if (page < 0 || page >= num_pages) atomicOr(err, kErrBadPage);
@@ -345,8 +359,9 @@ extern "C" int cie_attention_generic_split(const void* q, int q_stride, void* ou
                                            int num_pages, int tokens, int q_heads, int kv_heads, int dim,
                                            int vdim, int page_size, float scale, int window,
                                            const float* r1, const float* r2, int splits, float* shares,
-                                           int* tickets, int dtype, int* err, void* stream) {
+                                           int* tickets, int keep_first, int dtype, int* err, void* stream) {
   if (tokens <= 0) return 0;
+  if (keep_first < 0) CIE_FAIL("attention_generic: %d kept keys", keep_first);
   if (splits < 1 || (splits > 1 && (!shares || !tickets))) CIE_FAIL("attention_generic: %d key ranges need shares and tickets", splits);
   if (dim > kMaxDim || dim < 1 || vdim > kMaxDim || vdim < 1)
     CIE_FAIL("attention_generic: head sizes %d / %d are outside 1..%d", dim, vdim, kMaxDim);
@@ -376,7 +391,7 @@ extern "C" int cie_attention_generic_split(const void* q, int q_stride, void* ou
     CIE_LAUNCH("attention_group", (attention_group_kernel<T, S>), grid, dim3(kGroupWarps * 32), smem, s,            \
                (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, positions,          \
                request_of_token, table, table_width, num_pages, q_heads, kv_heads, dim, vdim, page_size, scale,    \
-               window, r1, r2, splits, shares, tickets, err);                                                      \
+               window, keep_first, r1, r2, splits, shares, tickets, err);                                          \
   } while (0)
     if (dtype == kFloat32) CIE_GROUP(float, false);
     else if (staged) CIE_GROUP(__nv_bfloat16, true);
@@ -388,12 +403,12 @@ extern "C" int cie_attention_generic_split(const void* q, int q_stride, void* ou
     CIE_LAUNCH("attention_generic", attention_generic_kernel<float>, dim3(blocks), dim3(kWarps * 32), 0, s,
         (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,
         positions, request_of_token, table, table_width, num_pages, tokens, q_heads, kv_heads, dim, vdim,
-        page_size, scale, window, r1, r2, err);
+        page_size, scale, window, keep_first, r1, r2, err);
   } else if (dtype == kBFloat16) {
     CIE_LAUNCH("attention_generic", attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(kWarps * 32), 0, s,
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
         (const __nv_bfloat16*)v_pool, positions, request_of_token, table, table_width, num_pages, tokens,
-        q_heads, kv_heads, dim, vdim, page_size, scale, window, r1, r2, err);
+        q_heads, kv_heads, dim, vdim, page_size, scale, window, keep_first, r1, r2, err);
   } else {
     CIE_FAIL("attention_generic: unknown element type code %d", dtype);
   }
@@ -409,7 +424,7 @@ extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, 
                                         void* stream) {
   return cie_attention_generic_split(q, q_stride, out, out_stride, k_pool, v_pool, positions, request_of_token,
                                      table, table_width, num_pages, tokens, q_heads, kv_heads, dim, vdim,
-                                     page_size, scale, window, r1, r2, 1, nullptr, nullptr, dtype, err, stream);
+                                     page_size, scale, window, r1, r2, 1, nullptr, nullptr, 0, dtype, err, stream);
 }
 
 extern "C" int cie_attention_generic(const void* q, int q_stride, void* out, int out_stride,

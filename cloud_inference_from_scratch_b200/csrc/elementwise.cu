@@ -509,6 +509,83 @@ __global__ void gated_act_kernel(const TI* __restrict__ gate_up, const float* __
   }
 }
 
+// ---------------------------------------------------------------- embedding + sinusoid of the position
+// residual[t] = table[ids[t]] * scale + wave(positions[t]): entry 2i of the wave is sin(p * freq[i]), entry
+// 2i + 1 is cos(p * freq[i]); `freq` holds ceil(hidden / 2) float32 frequencies (rounded once from double on
+// the host).  The angle is the float32 product of the position and the frequency.
+template <typename T>
+__global__ void embedding_wave_kernel(const int* __restrict__ ids, const int* __restrict__ positions,
+                                      const T* __restrict__ table, const float* __restrict__ freq,
+                                      float* __restrict__ residual, int hidden, int vocab, float scale, int* err) {
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicOr(err, kErrBadToken);
+    id = 0;
+  }
+  const float p = (float)positions[t];
+  const T* row = table + (size_t)id * hidden;
+  float* out = residual + (size_t)t * hidden;
+  for (int pair = threadIdx.x; 2 * pair < hidden; pair += blockDim.x) {
+    float s, c;
+    sincosf(p * freq[pair], &s, &c);
+    out[2 * pair] = fmaf(to_float(row[2 * pair]), scale, s);
+    if (2 * pair + 1 < hidden) out[2 * pair + 1] = fmaf(to_float(row[2 * pair + 1]), scale, c);
+  }
+}
+
+// ---------------------------------------------------------------- a vector added to every row of the stream
+// residual[t][i] += vec[i] (+ the pending update: float32 terms [splits][rows][hidden] `stride` apart, added in
+// ascending order).  What a run of layers that starts with a learned offset does before its first norm.
+__global__ void add_rows_kernel(float* __restrict__ residual, const float* __restrict__ update, int splits,
+                                size_t stride, const float* __restrict__ vec, int hidden, size_t total) {
+  pdl_wait();
+  pdl_trigger();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    float x = residual[e];
+    if (update) x += sum_partials(update + e, splits, stride);
+    residual[e] = x + vec[e % hidden];
+  }
+}
+
+// ---------------------------------------------------------------- activations of one input
+// out = act(x) for float32 x, rounded once.  kind 0: relu(x)^2.
+template <typename T>
+__global__ void unary_act_kernel(const float* __restrict__ x, T* __restrict__ out, size_t total, int kind) {
+  pdl_wait();
+  pdl_trigger();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const float v = fmaxf(x[e], 0.f);
+    out[e] = from_float<T>(v * v);
+  }
+}
+
+// x[t][c] *= sigmoid(gate[t * gate_stride + c]) in float32, rounded once; the gate is a view of columns of a
+// wider row.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, const T* __restrict__ gate, int gate_stride, int width,
+                                    size_t total) {
+  pdl_wait();
+  pdl_trigger();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = e / width;
+    const int c = (int)(e % width);
+    const float z = to_float(gate[t * gate_stride + c]);
+    x[e] = from_float<T>(to_float(x[e]) / (1.f + expf(-z)));
+  }
+}
+
+// out = alpha * a (+ beta * out when beta != 0), float32.
+__global__ void scaled_sum_kernel(float* __restrict__ out, const float* __restrict__ a, float alpha, float beta,
+                                  size_t total) {
+  pdl_wait();
+  pdl_trigger();
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x)
+    out[e] = beta != 0.f ? fmaf(alpha, a[e], beta * out[e]) : alpha * a[e];
+}
+
 }  // namespace cie
 
 using namespace cie;
@@ -531,6 +608,60 @@ extern "C" int cie_embedding(const int* ids, const void* table, float* residual,
     CIE_LAUNCH("embedding", embedding_kernel<T>, dim3(tokens), dim3(threads_for(hidden / 4)), 0,
                (cudaStream_t)stream, ids, (const T*)table, residual, hidden, vocab, scale, err);
   })
+  return 0;
+}
+
+static int blocks_for(size_t total) {
+  size_t blocks = (total + 255) / 256;
+  return (int)(blocks > 148 * 16 ? 148 * 16 : blocks);
+}
+
+extern "C" int cie_embedding_wave(const int* ids, const int* positions, const void* table, const float* freq,
+                                  float* residual, int tokens, int hidden, int vocab, float scale, int dtype,
+                                  int* err, void* stream) {
+  if (tokens <= 0) return 0;
+  DISPATCH_DTYPE(dtype, "embedding_wave", {
+    CIE_LAUNCH("embedding_wave", embedding_wave_kernel<T>, dim3(tokens), dim3(threads_for(hidden / 2)), 0,
+               (cudaStream_t)stream, ids, positions, (const T*)table, freq, residual, hidden, vocab, scale, err);
+  })
+  return 0;
+}
+
+extern "C" int cie_add_rows(float* residual, const float* update, int splits, long long stride, const float* vec,
+                            int tokens, int hidden, void* stream) {
+  if (tokens <= 0) return 0;
+  if (update && (splits < 1 || splits > kMaxSplits)) CIE_FAIL("add_rows: %d terms of an update", splits);
+  const size_t total = (size_t)tokens * hidden;
+  CIE_LAUNCH("add_rows", add_rows_kernel, dim3(blocks_for(total)), dim3(256), 0, (cudaStream_t)stream, residual,
+             update, splits, (size_t)stride, vec, hidden, total);
+  return 0;
+}
+
+extern "C" int cie_unary_act(const float* x, void* out, long long total, int kind, int dtype, void* stream) {
+  if (total <= 0) return 0;
+  if (kind != 0) CIE_FAIL("unary_act: unknown activation %d", kind);
+  DISPATCH_DTYPE(dtype, "unary_act", {
+    CIE_LAUNCH("unary_act", unary_act_kernel<T>, dim3(blocks_for((size_t)total)), dim3(256), 0,
+               (cudaStream_t)stream, x, (T*)out, (size_t)total, kind);
+  })
+  return 0;
+}
+
+extern "C" int cie_sigmoid_gate(void* x, const void* gate, int gate_stride, int tokens, int width, int dtype,
+                                void* stream) {
+  if (tokens <= 0) return 0;
+  const size_t total = (size_t)tokens * width;
+  DISPATCH_DTYPE(dtype, "sigmoid_gate", {
+    CIE_LAUNCH("sigmoid_gate", sigmoid_gate_kernel<T>, dim3(blocks_for(total)), dim3(256), 0, (cudaStream_t)stream,
+               (T*)x, (const T*)gate, gate_stride, width, total);
+  })
+  return 0;
+}
+
+extern "C" int cie_scaled_sum(float* out, const float* a, float alpha, float beta, long long total, void* stream) {
+  if (total <= 0) return 0;
+  CIE_LAUNCH("scaled_sum", scaled_sum_kernel, dim3(blocks_for((size_t)total)), dim3(256), 0, (cudaStream_t)stream,
+             out, a, alpha, beta, (size_t)total);
   return 0;
 }
 

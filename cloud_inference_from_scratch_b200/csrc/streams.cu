@@ -133,7 +133,7 @@ __global__ void norm_kv_write_kernel(const T* __restrict__ src, const float* __r
                                      T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const float* __restrict__ q_gain, const float* __restrict__ k_gain,
                                      int q_heads, int kv_heads, int dim, int vdim, int page_size,
-                                     int qk_norm, int v_norm, float eps, int write_cache, int* err) {
+                                     int qk_norm, int v_norm, float eps, int write_cache, int src_stride, int* err) {
   extern __shared__ float row_s[];
   __shared__ float scratch[33];
   pdl_wait();
@@ -141,7 +141,7 @@ __global__ void norm_kv_write_kernel(const T* __restrict__ src, const float* __r
   const int t = blockIdx.x;
   const int q_width = q_heads * dim, k_width = kv_heads * dim, v_width = kv_heads * vdim;
   const int width = q_width + k_width + v_width;
-  const T* row = src + (size_t)t * width;
+  const T* row = src + (size_t)t * src_stride;
   float sq_q = 0.f, sq_k = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float v = to_float(row[i]);
@@ -152,13 +152,27 @@ __global__ void norm_kv_write_kernel(const T* __restrict__ src, const float* __r
   }
   __syncthreads();
   float inv_q = 1.f, inv_k = 1.f;
-  if (qk_norm) {
+  if (qk_norm == 1) {
     inv_q = rsqrtf(block_sum(sq_q, scratch) / (float)q_width + eps);
     inv_k = rsqrtf(block_sum(sq_k, scratch) / (float)k_width + eps);
+  } else if (qk_norm == 2) {
+    // every q and k head by its own root mean square, times a gain vector of the head's size that all heads
+    // share; a warp takes a head at a time and leaves the finished head in the staged row
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, ws = blockDim.x >> 5;
+    for (int h = w; h < q_heads + kv_heads; h += ws) {
+      float* head = row_s + (size_t)h * dim;
+      const float* gain = h < q_heads ? q_gain : k_gain;
+      float sq = 0.f;
+      for (int d = l; d < dim; d += 32) sq = fmaf(head[d], head[d], sq);
+      const float inv = rsqrtf(warp_sum(sq) / (float)dim + eps);
+      for (int d = l; d < dim; d += 32) head[d] = gain[d] * (head[d] * inv);
+    }
+    __syncthreads();
   }
+  const bool whole = qk_norm == 1;     // q and k are still to be scaled by the norm over their whole projection
   T* q_row = q_out + (size_t)t * q_stride;
   for (int i = threadIdx.x; i < q_width; i += blockDim.x)
-    q_row[i] = from_float<T>(qk_norm ? q_gain[i] * (row_s[i] * inv_q) : row_s[i]);
+    q_row[i] = from_float<T>(whole ? q_gain[i] * (row_s[i] * inv_q) : row_s[i]);
   if (!write_cache) return;
   const int pos = positions[t];
   const int request = request_of_token[t];
@@ -172,7 +186,7 @@ __global__ void norm_kv_write_kernel(const T* __restrict__ src, const float* __r
   const float* k_row = row_s + q_width;
   for (int i = threadIdx.x; i < k_width; i += blockDim.x) {
     const int h = i / dim, d = i % dim;
-    const float v = qk_norm ? k_gain[i] * (k_row[i] * inv_k) : k_row[i];
+    const float v = whole ? k_gain[i] * (k_row[i] * inv_k) : k_row[i];
     k_pool[(slot + (size_t)h * page_size) * dim + d] = from_float<T>(v);
   }
   // value heads: a warp per head at a time
@@ -266,17 +280,23 @@ extern "C" int cie_norm_kv_write(const void* src, const float* bias, void* q_out
                                  int table_width, int num_pages, void* k_pool, void* v_pool,
                                  const float* q_gain, const float* k_gain, int tokens, int q_heads,
                                  int kv_heads, int dim, int vdim, int page_size, int qk_norm, int v_norm,
-                                 float eps, int write_cache, int dtype, int* err, void* stream) {
+                                 float eps, int write_cache, int src_stride, int dtype, int* err, void* stream) {
+  // qk_norm: 0 none; 1 over the whole projection (gains of the projection's size); 2 per head (gains of a
+  // head's size, shared by the heads).  src_stride: elements from one source row to the next (0: the
+  // row holds q, k and v and nothing else).
   if (tokens <= 0) return 0;
   if (qk_norm && (!q_gain || !k_gain)) CIE_FAIL("norm_kv_write: the q/k norm needs its gains");
+  if (qk_norm < 0 || qk_norm > 2) CIE_FAIL("norm_kv_write: unknown q/k norm %d", qk_norm);
   const int width = q_heads * dim + kv_heads * (dim + vdim);
+  if (src_stride == 0) src_stride = width;
+  if (src_stride < width) CIE_FAIL("norm_kv_write: source rows of %d elements are shorter than q, k and v (%d)", src_stride, width);
   const size_t smem = (size_t)width * sizeof(float);
   DISPATCH_DTYPE(dtype, "norm_kv_write", {
     if (allow_shared(norm_kv_write_kernel<T>, smem, "norm_kv_write")) return 1;
     CIE_LAUNCH("norm_kv_write", norm_kv_write_kernel<T>, dim3(tokens), dim3(256), smem, (cudaStream_t)stream,
                (const T*)src, bias, (T*)q_out, q_stride, positions, request_of_token, table, table_width,
                num_pages, (T*)k_pool, (T*)v_pool, q_gain, k_gain, q_heads, kv_heads, dim, vdim, page_size,
-               qk_norm, v_norm, eps, write_cache, err);
+               qk_norm, v_norm, eps, write_cache, src_stride, err);
   })
   return 0;
 }

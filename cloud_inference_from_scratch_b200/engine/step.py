@@ -169,11 +169,17 @@ class StepFunction:
         """Mixers may add integer work lists of their own to a step's metadata: a mixer with
         ``plan_key`` and ``plan(host, cache)`` is asked once per distinct key."""
         planners: dict[Any, Any] = {}
+
+        def visit(part: Any) -> None:
+            key = getattr(part, "plan_key", None)
+            if key is not None and key not in planners:
+                planners[key] = part
+            for inner in getattr(part, "subparts", lambda: ())():
+                visit(inner)
+
         for layer in self.model.layers:
             for part in layer.parts.values():
-                key = getattr(part, "plan_key", None)
-                if key is not None and key not in planners:
-                    planners[key] = part
+                visit(part)
         return planners
 
     def enable_graphs(self, max_model_len: int) -> None:

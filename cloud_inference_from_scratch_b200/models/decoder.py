@@ -9,9 +9,10 @@ the rows whose logits are wanted (the reference normalises all rows and then sel
 model.py:221-225), multiply by the head and return float32 logits.
 
 Beyond the reference: a description may ask for a learned vector per position that is added to the
-embedding rows (``position_tensor``) and for several copies of the residual stream side by side
-(``residual_streams``, [T, streams * H]); the blocks of such a model read and write the copies and
-the final norm reads their sum.
+embedding rows (``position_tensor``), for a sinusoid of the position instead (``position_wave_base``),
+for several copies of the residual stream side by side (``residual_streams``, [T, streams * H]; the
+blocks of such a model read and write the copies and the final norm reads their sum), and for a stored
+vector that is added to the stream right before a run of a layer (``ScheduleEntry.entry_offset``).
 """
 
 from __future__ import annotations
@@ -104,6 +105,9 @@ class DecoderModel:
         self.records_programs = all(
             getattr(part, "kernels_through_ops", False)
             for layer in self.layers for part in [layer.block, *layer.parts.values()])
+        # a callable (schedule entry, residual, pending update) run after every layer, for whoever wants to look
+        # at the stream (tests); the stream after the layer is ``residual`` plus what is still pending
+        self.after_layer: Any = None
         self.embedding: Any = None
         self.position_table: Any = None
         self.head: Any = None
@@ -120,6 +124,8 @@ class DecoderModel:
             table[spec.head_tensor] = TensorSpec((spec.vocab_size, spec.hidden_size))
         if spec.position_tensor:
             table[spec.position_tensor] = TensorSpec((spec.max_positions, spec.hidden_size))
+        for name, rows in spec.offset_tensors:
+            table[name] = TensorSpec((rows, spec.hidden_size), role="vector")
         for layer in self.layers:
             for prefix, part in layer.named_parts():
                 for name, tensor in part.tensor_specs().items():
@@ -159,6 +165,16 @@ class DecoderModel:
             if spec.head_tensor == spec.embedding_tensor
             else runtime.ops.prepare_weight(tensors(spec.head_tensor))
         )
+        self.offsets = {name: tensors(name).contiguous() for name, _ in spec.offset_tensors}
+        self.wave = None
+        if spec.position_wave_base is not None:
+            import torch
+
+            # frequencies in double precision, rounded once; the kernel multiplies by the position in float32
+            pairs = torch.arange((spec.hidden_size + 1) // 2, dtype=torch.float64)
+            wave = torch.pow(torch.tensor(float(spec.position_wave_base), dtype=torch.float64),
+                             -2.0 * pairs / spec.hidden_size)
+            self.wave = wave.to(device=runtime.device, dtype=torch.float32).contiguous()
         for layer in self.layers:
             for prefix, part in layer.named_parts():
                 part.bind({name: tensors(prefix + name) for name in part.tensor_specs()}, runtime)
@@ -176,7 +192,10 @@ class DecoderModel:
         spec = self.spec
         streams = spec.residual_streams
         residual = rt.workspace.get("residual", ctx.num_tokens, spec.hidden_size * streams, torch.float32)
-        if streams > 1 or self.position_table is not None:
+        if self.wave is not None:
+            rt.ops.embedding(ctx.token_ids, self.embedding, residual, spec.embedding_scale,
+                             positions=ctx.positions, wave=self.wave)
+        elif streams > 1 or self.position_table is not None:
             # the stream copies lie side by side in a token's row; a learned position vector is added
             rt.ops.embedding(ctx.token_ids, self.embedding, residual, spec.embedding_scale,
                              positions=ctx.positions, position_table=self.position_table, streams=streams)
@@ -193,9 +212,15 @@ class DecoderModel:
                 sink.following_gain = None
                 if index + 1 < len(spec.schedule):
                     sink.following_gain = self.layers[spec.schedule[index + 1].layer].block.entry_gain()
+            if entry.entry_offset is not None:
+                name, row = entry.entry_offset
+                rt.ops.add_rows(residual, pending, self.offsets[name][row])
+                pending = None
             pending = self.layers[entry.layer].block.forward(
                 residual, pending, ctx, ctx.bindings[index]
             )
+            if self.after_layer is not None:
+                self.after_layer(index, residual, pending)
         if recorded:
             rt.ops.end_program()
         if ctx.num_logit_rows == 0:

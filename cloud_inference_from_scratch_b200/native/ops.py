@@ -97,6 +97,11 @@ class Ops:
         )
         self._silu_mul = ew.function("cie_silu_mul", [v, v, i, i, i, i, v])
         self._gated_act = ew.function("cie_gated_act", [v, i, v, v, i, i, f, f, f, i, v])
+        self._embedding_wave = ew.function("cie_embedding_wave", [v, v, v, v, v, i, i, i, f, i, v, v])
+        self._add_rows = ew.function("cie_add_rows", [v, v, i, ll, v, i, i, v])
+        self._unary_act = ew.function("cie_unary_act", [v, v, ll, i, i, v])
+        self._sigmoid_gate = ew.function("cie_sigmoid_gate", [v, v, i, i, i, i, v])
+        self._scaled_sum = ew.function("cie_scaled_sum", [v, v, f, f, ll, v])
         gs = _Lib(load_library("gemm_simt.cu"))
         self._gemm_simt = gs.function("cie_gemm_simt", [v, v, v, v, i, i, i, i, i, i, v])
         ag = _Lib(load_library("attention_generic.cu"))
@@ -110,7 +115,7 @@ class Ops:
         )
         self._attention_generic_split = ag.function(
             "cie_attention_generic_split",
-            [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, i, f, i, v, v, i, v, v, i, v, v],
+            [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, i, f, i, v, v, i, v, v, i, i, v, v],
         )
         self._group_share_floats = int(ag.handle.cie_attention_group_share_floats())
         self._group_tickets = None
@@ -119,6 +124,7 @@ class Ops:
         self._lightning_lib = None
         self._latent_lib = None
         self._delta_lib = None
+        self._recurrent_lib = None
         self._moe_lib = None
         self._sample = None   # sampling.cu is built when something is first sampled
         self._tensor_gemm = None
@@ -206,19 +212,21 @@ class Ops:
         return weight.to(device=self.device, dtype=self.dtype).contiguous()
 
     def attention_penalised(self, q: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
-                            head_dim: int, value_dim: int, scale: float, window: int, distance: Any) -> None:
+                            head_dim: int, value_dim: int, scale: float, window: int, distance: Any,
+                            keep_first: int = 0) -> None:
         """Attention with the options of ``attention_generic`` (a value size of its own, a distance
         penalty), softmax weights float32 throughout.  bfloat16 prompt portions whose value heads have
         the size of the key heads run on the tensor cores (mma.sync; the weights enter the value
         product as two bfloat16 terms); single tokens, the 32-bit path and every other shape run on
         the kernel that takes one warp per (token, head)."""
-        fast = self._tensor_attention.get(head_dim) if value_dim == head_dim and self.code == BF16 else None
+        fast = (self._tensor_attention.get(head_dim)
+                if value_dim == head_dim and self.code == BF16 and not keep_first else None)
         singles = ctx.num_single
         if (fast is None or singles == ctx.num_requests or q.shape[1] % 8 or out.shape[1] % 8
                 or os.environ.get("CIE_PENALISED_TC", "1") == "0"):
             self.attention_generic(q, out, ctx, kv, q_heads, kv_heads, head_dim, scale, window,
                                    value_dim=value_dim, distance=distance,
-                                   few_tokens=singles == ctx.num_requests)
+                                   few_tokens=singles == ctx.num_requests, keep_first=keep_first)
             return
         if singles:     # the leading rows of a mixed step are its single tokens
             self.attention_generic(q[:singles], out[:singles], ctx, kv, q_heads, kv_heads, head_dim, scale,
@@ -259,13 +267,22 @@ class Ops:
 
     # ------------------------------------------------------------------ kernels
     def embedding(self, token_ids: Any, table: Any, residual: Any, scale: float = 1.0,
-                  positions: Any = None, position_table: Any = None, streams: int = 1) -> None:
+                  positions: Any = None, position_table: Any = None, streams: int = 1,
+                  wave: Any = None) -> None:
         """residual[t] = table[token_ids[t]] * scale (+ position_table[positions[t]]), float32, in each
-        of ``streams`` side-by-side copies ([T, streams * H])."""
+        of ``streams`` side-by-side copies ([T, streams * H]).  ``wave``: float32 frequencies [ceil(H / 2)];
+        then sin(p * wave[i]) is added to entry 2i and cos(p * wave[i]) to entry 2i + 1, p the position."""
         self._flush()
         tokens = residual.shape[0]
         hidden = residual.shape[1] // streams
         self.launches += 1
+        if wave is not None:
+            if position_table is not None or streams > 1:
+                raise KernelError("embedding: a sinusoid goes with one stream and no learned position vector")
+            self._embedding_wave(_ptr(token_ids), _ptr(positions), _ptr(table), _ptr(wave), _ptr(residual), tokens,
+                                 hidden, table.shape[0], float(scale), self._code_of(table), _ptr(self.error_word),
+                                 self.stream)
+            return
         if position_table is not None or streams > 1:
             self._load_streams()
             self._embedding_streams(_ptr(token_ids), _ptr(positions), _ptr(table), _ptr(position_table),
@@ -298,6 +315,10 @@ class Ops:
             update = None   # its kernel has added it already
         if isinstance(update, Partials) and update.splits == 0:
             update = self.resolve(update, None)
+        if (update is not None and not isinstance(update, Partials) and update.dtype == self.torch.float32
+                and self.code != F32):
+            # a float32 result in a bfloat16 run: one float32 term still to be added
+            update = Partials(update, 1, update.shape[0], update.shape[1], None)
         if isinstance(update, Partials):
             self._add_rmsnorm(_ptr(residual), _ptr(update.data), update.splits,
                               update.stride, _ptr(update.bias), _ptr(gain), _ptr(out),
@@ -305,6 +326,134 @@ class Ops:
         else:
             self._add_rmsnorm(_ptr(residual), _ptr(update), 0, 0, None, _ptr(gain), _ptr(out),
                               _ptr(rows), count, hidden, eps, self._code_of(out), self.stream)
+
+    def add_rows(self, residual: Any, update: Any, vector: Any) -> None:
+        """residual[t] += vector (+ ``update``: None, an ``Accumulated`` (already added), or float32 terms as
+        ``Partials``), float32 in place: the stream as a run of layers that starts with a learned offset
+        finds it."""
+        self._flush()
+        if isinstance(update, Accumulated):
+            update = None
+        if update is not None and not isinstance(update, Partials):
+            if update.dtype != self.torch.float32:
+                update = update.float()
+            update = Partials(update.contiguous(), 1, update.shape[0], update.shape[1], None)
+        if isinstance(update, Partials) and (update.splits == 0 or update.bias is not None):
+            data = self.resolve(update, self.torch.empty(update.shape, dtype=self.torch.float32, device=self.device))
+            update = Partials(data.float().contiguous(), 1, update.rows, update.width, None)
+        tokens, hidden = residual.shape
+        self.launches += 1
+        if update is None:
+            self._add_rows(_ptr(residual), None, 0, 0, _ptr(vector), tokens, hidden, self.stream)
+        else:
+            self._add_rows(_ptr(residual), _ptr(update.data), update.splits, update.stride, _ptr(vector), tokens,
+                           hidden, self.stream)
+
+    def unary_act(self, x: Any, out: Any, kind: str = "relu2") -> None:
+        """out = act(x) for contiguous float32 ``x``, rounded once; "relu2": the square of relu."""
+        self._flush()
+        kinds = {"relu2": 0}
+        if kind not in kinds:
+            raise KernelError(f"unary_act: unknown activation {kind!r} (known: {sorted(kinds)})")
+        self.launches += 1
+        self._unary_act(_ptr(x), _ptr(out), x.numel(), kinds[kind], self._code_of(out), self.stream)
+
+    def sigmoid_gate(self, x: Any, gate: Any) -> None:
+        """x *= sigmoid(gate) in place; ``gate`` is a view of columns of a wider row of the same dtype."""
+        self._flush()
+        self.launches += 1
+        self._sigmoid_gate(_ptr(x), _ptr(gate), gate.stride(0), x.shape[0], x.shape[1], self._code_of(x), self.stream)
+
+    def scaled_sum(self, out: Any, a: Any, alpha: float, accumulate: bool) -> None:
+        """out = alpha * a, or out += alpha * a; contiguous float32."""
+        self._flush()
+        self.launches += 1
+        self._scaled_sum(_ptr(out), _ptr(a), float(alpha), 1.0 if accumulate else 0.0, a.numel(), self.stream)
+
+    # ------------------------------------------------------------------ recurrent mixers with one gate a head
+    def _load_recurrent(self) -> None:
+        if self._recurrent_lib is None:
+            v, i, f, ll = c_void_p, c_int, c_float, ctypes.c_longlong
+            lib = _Lib(load_library("recurrent.cu"))
+            self._mlstm_scan = lib.function(
+                "cie_mlstm_scan", [v, i, i, i, i, i, i, v, v, f, f, v, i, v, ll, v, v, v, i, i, i, i, i, v, v])
+            self._gated_delta_scan = lib.function(
+                "cie_gated_delta_scan", [v, i, i, i, i, v, i, i, i, v, v, f, v, i, v, ll, v, v, v, i, i, i, i, i, i, v, v])
+            self._short_conv = lib.function("cie_short_conv", [v, i, v, i, v, ll, v, i, v, v, v, v, i, i, i, i, v, v])
+            self._head_norm_gate = lib.function("cie_head_norm_gate", [v, i, v, i, v, i, i, v, i, i, i, i, f, i, v])
+            self.scan_max_dim = int(lib.handle.cie_scan_max_dim())
+            self.conv_max_taps = int(lib.handle.cie_conv_max_taps())
+            self._recurrent_lib = lib
+
+    def require_recurrent(self) -> tuple[int, int]:
+        """Builds, at model set-up, the kernels of the recurrent mixers with one gate a head; returns the largest
+        key size and the longest short convolution they take."""
+        self._load_recurrent()
+        return self.scan_max_dim, self.conv_max_taps
+
+    def mlstm_scan(self, proj: Any, offsets: tuple[int, int, int, int, int], input_bias: Any, forget_bias: Any,
+                   cap: float, q_scale: float, out: Any, state: Any, ctx: Any, heads: int, dim: int, vdim: int) -> None:
+        """Runs the matrix memory (mLSTM) over every request's new tokens from the state in its slot
+        (``state``: float32 [slots, heads * (dim * vdim + dim + 1)]: per head the matrix, the normaliser and
+        the running maximum).  ``proj`` float32 rows hold q, k, v and the two gate projections from the
+        columns ``offsets``; ``out`` float32 [T, heads * vdim]."""
+        self._flush()
+        self._load_recurrent()
+        q_off, k_off, v_off, i_off, f_off = offsets
+        self.launches += 1
+        self._mlstm_scan(_ptr(proj), proj.stride(0), q_off, k_off, v_off, i_off, f_off, _ptr(input_bias),
+                         _ptr(forget_bias), float(cap), float(q_scale), _ptr(out), out.stride(0), _ptr(state),
+                         state.stride(0), _ptr(ctx.query_start), _ptr(ctx.slots), _ptr(ctx.request_active),
+                         ctx.num_requests, heads, dim, vdim, state.shape[0], _ptr(self.error_word), self.stream)
+
+    def short_conv(self, proj: Any, weight: Any, history: Any, out: Any, ctx: Any) -> None:
+        """out[t, c] = silu(sum_j weight[c, j] * x[t - (taps - 1 - j), c]) for the first ``weight.shape[0]``
+        columns of float32 ``proj``; inputs before this step come from ``history`` (a view [slots, (taps - 1) *
+        channels] of the requests' state, oldest first), which then takes this step's last inputs."""
+        self._flush()
+        self._load_recurrent()
+        channels, taps = weight.shape
+        self.launches += 2 if taps > 1 else 1
+        self._short_conv(_ptr(proj), proj.stride(0), _ptr(weight), taps, _ptr(history), history.stride(0), _ptr(out),
+                         out.stride(0), _ptr(ctx.query_start), _ptr(ctx.request_of_token), _ptr(ctx.slots),
+                         _ptr(ctx.request_active), proj.shape[0], ctx.num_requests, channels, history.shape[0],
+                         _ptr(self.error_word), self.stream)
+
+    def gated_delta_scan(self, conv: Any, offsets: tuple[int, int, int], proj: Any, gate_offsets: tuple[int, int],
+                         a_log: Any, dt_bias: Any, q_scale: float, out: Any, state: Any, ctx: Any, heads: int,
+                         kv_heads: int, dim: int, vdim: int) -> None:
+        """Runs the gated delta rule over every request's new tokens from the state in its slot (``state``:
+        float32 [slots, >= heads * dim * vdim], a head's matrix after the other).  ``conv`` float32 rows hold
+        q, k (kv_heads x dim) and v (heads x vdim) after convolution and SiLU from the columns ``offsets``;
+        ``proj`` float32 rows hold the write-strength and decay projections (heads each) from ``gate_offsets``;
+        ``out`` float32 [T, heads * vdim]."""
+        self._flush()
+        self._load_recurrent()
+        q_off, k_off, v_off = offsets
+        b_off, a_off = gate_offsets
+        self.launches += 1
+        self._gated_delta_scan(_ptr(conv), conv.stride(0), q_off, k_off, v_off, _ptr(proj), proj.stride(0), b_off,
+                               a_off, _ptr(a_log), _ptr(dt_bias), float(q_scale), _ptr(out), out.stride(0),
+                               _ptr(state), state.stride(0), _ptr(ctx.query_start), _ptr(ctx.slots),
+                               _ptr(ctx.request_active), ctx.num_requests, heads, kv_heads, dim, vdim,
+                               state.shape[0], _ptr(self.error_word), self.stream)
+
+    def head_norm_gate(self, o: Any, gate: Any, gain: Any, eps: float, out: Any, heads: int,
+                       gate_act: str = "sigmoid") -> None:
+        """Every head (``out.shape[1] / heads`` columns) of float32 ``o`` divided by its own root mean square,
+        times ``gain`` (one number per column, or a vector of a head's size for all heads), times sigmoid or
+        SiLU of ``gate`` (float32, may be a view of columns)."""
+        self._flush()
+        self._load_recurrent()
+        size = out.shape[1] // heads
+        if gain.numel() not in (size, out.shape[1]):
+            raise KernelError(f"head_norm_gate: a gain of {gain.numel()} numbers for heads of {size}")
+        shared = 1 if gain.numel() == size and heads > 1 else 0
+        acts = {"sigmoid": 0, "silu": 1}
+        self.launches += 1
+        self._head_norm_gate(_ptr(o), o.stride(0), _ptr(gate), gate.stride(0), _ptr(gain), shared, acts[gate_act],
+                             _ptr(out), out.stride(0), out.shape[0], heads, size, float(eps), self._code_of(out),
+                             self.stream)
 
     # ------------------------------------------------------------------ residual streams
     def _load_streams(self) -> None:
@@ -314,7 +463,7 @@ class Ops:
             self._embedding_streams = lib.function("cie_embedding_streams", [v, v, v, v, v, i, i, i, i, i, f, i, v, v])
             self._stream_norm = lib.function("cie_stream_norm", [v, i, v, i, v, v, v, v, i, v, v, i, i, f, i, v])
             self._norm_kv_write = lib.function(
-                "cie_norm_kv_write", [v, v, v, i, v, v, v, i, i, v, v, v, v, i, i, i, i, i, i, i, i, f, i, i, v, v])
+                "cie_norm_kv_write", [v, v, v, i, v, v, v, i, i, v, v, v, v, i, i, i, i, i, i, i, i, f, i, i, i, v, v])
             self._streams_lib = lib
 
     def stream_norm(self, residual: Any, streams: int, update: Any, read: Any, gain: Any, eps: float,
@@ -345,11 +494,14 @@ class Ops:
 
     def norm_kv_write(self, qkv: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int, dim: int, vdim: int,
                       q_gain: Any, k_gain: Any, value_norm: bool, eps: float, q_buffer: Any,
-                      write_cache: bool = True) -> Any:
+                      write_cache: bool = True, per_head: bool = False) -> Any:
         """q and k of every token divided by the root mean square of their whole projection and
         multiplied by a gain vector (``q_gain`` None: left as they are), every value head divided by
         its own root mean square (``value_norm``); q goes to ``q_buffer``, k and v into the pages.
-        ``qkv`` is a tensor [T, (Hq + Hkv) * dim + Hkv * vdim] or ``Partials`` with its bias pending."""
+        ``per_head``: every q and k head is divided by its OWN root mean square instead, and the gains
+        are vectors of a head's size that all heads share.
+        ``qkv`` is a tensor [T, (Hq + Hkv) * dim + Hkv * vdim] (its rows may go on with other columns,
+        which are left alone) or ``Partials`` with its bias pending."""
         self._flush()
         self._load_streams()
         bias = None
@@ -363,8 +515,9 @@ class Ops:
         self._norm_kv_write(_ptr(qkv), _ptr(bias), _ptr(q_buffer), q_buffer.shape[1], _ptr(ctx.positions),
                             _ptr(ctx.request_of_token), _ptr(table), table.shape[1], kv.num_pages, _ptr(kv.k),
                             _ptr(kv.v), _ptr(q_gain), _ptr(k_gain), qkv.shape[0], q_heads, kv_heads, dim, vdim,
-                            kv.page_size, 1 if q_gain is not None else 0, 1 if value_norm else 0, float(eps),
-                            1 if write_cache else 0, self._code_of(qkv), _ptr(self.error_word), self.stream)
+                            kv.page_size, 0 if q_gain is None else (2 if per_head else 1), 1 if value_norm else 0,
+                            float(eps), 1 if write_cache else 0, qkv.stride(0), self._code_of(qkv),
+                            _ptr(self.error_word), self.stream)
         return q_buffer
 
     # ------------------------------------------------------------------ linear attention with decay
@@ -1086,8 +1239,10 @@ class Ops:
 
     def attention_generic(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int,
                           kv_heads: int, head_dim: int, scale: float, window: int,
-                          value_dim: int | None = None, distance: Any = None, few_tokens: bool = False) -> None:
-        """``value_dim``: size of a value head when it is not ``head_dim``; ``distance``: (r1, r2),
+                          value_dim: int | None = None, distance: Any = None, few_tokens: bool = False,
+                          keep_first: int = 0) -> None:
+        """``keep_first``: with a window, the request's first so many keys stay visible behind it.
+        ``value_dim``: size of a value head when it is not ``head_dim``; ``distance``: (r1, r2),
         float32 [q_heads] each, of the penalty r1 * log(1 + r2 * (query position - key position)).
         ``few_tokens``: the rows are single tokens of a decode step; their keys are then cut into
         ranges with a CTA each where the device would otherwise stand mostly idle."""
@@ -1099,7 +1254,7 @@ class Ops:
             units = tokens * kv_heads * -(-(q_heads // kv_heads) // 8)
             keys = table.shape[1] * kv.page_size
             if window > 0:
-                keys = min(keys, window)
+                keys = min(keys, window + keep_first)
             # a range keeps at least 128 keys; no more CTAs than one an SM
             splits = max(1, min(keys // 128, self.sm_count // max(units, 1), 16))
             if splits > 1:
@@ -1112,8 +1267,17 @@ class Ops:
                     _ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions),
                     _ptr(ctx.request_of_token), _ptr(table), table.shape[1], kv.num_pages, tokens, q_heads, kv_heads,
                     head_dim, value_dim or head_dim, kv.page_size, scale, window, _ptr(r1), _ptr(r2), splits,
-                    _ptr(shares), _ptr(self._group_tickets), self._code_of(qkv), _ptr(self.error_word), self.stream)
+                    _ptr(shares), _ptr(self._group_tickets), int(keep_first), self._code_of(qkv),
+                    _ptr(self.error_word), self.stream)
                 return
+        if keep_first:
+            r1, r2 = distance if distance is not None else (None, None)
+            self._attention_generic_split(
+                _ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions),
+                _ptr(ctx.request_of_token), _ptr(table), table.shape[1], kv.num_pages, qkv.shape[0], q_heads, kv_heads,
+                head_dim, value_dim or head_dim, kv.page_size, scale, window, _ptr(r1), _ptr(r2), 1, None, None,
+                int(keep_first), self._code_of(qkv), _ptr(self.error_word), self.stream)
+            return
         if distance is not None or (value_dim or head_dim) != head_dim:
             r1, r2 = distance if distance is not None else (None, None)
             self._attention_generic_ex(_ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k),

@@ -1,4 +1,7 @@
-from . import attention, block, connection, delta, latent, lightning, mlp, norm, rotary, routed  # noqa: F401  (registers the built-in parts)
+from . import (  # noqa: F401  (registers the built-in parts)
+    attention, block, connection, delta, gated_delta, latent, lightning, matrix_memory, mlp, norm, rotary, routed,
+    side_by_side,
+)
 from .base import (
     Block,
     CacheSpec,

@@ -19,14 +19,20 @@ Options beyond the reference, each a constant of the part so that any descriptio
 * ``qk_norm="projection"``: q and k are each divided by the root mean square of their whole
   projection (all heads together, before the split into heads) and multiplied by a stored gain
   vector of that size; keys are cached so;
+* ``qk_norm="head"``: every q and k head is divided by its OWN root mean square and multiplied by a
+  stored gain vector of a head's size that all heads share; keys are cached so;
 * ``value_norm``: every value head is divided by its own root mean square (no gain) before it is
   cached;
+* ``keep_first``: with a window, a query also sees the request's first ``keep_first`` keys (at their true
+  positions), however far the window has moved on;
+* ``gate``: the heads side by side are multiplied by ``sigmoid(W_g h)`` before the output projection
+  (the gate's weight is stacked under q, k and v: one product);
 * ``distance_penalty``: the score of query position i and key position j is lowered by
   ``r1_h * ln(1 + r2_h * (i - j))`` with two stored numbers per query head;
 * ``position=None``: no rotation;
 * ``names``: the tensor names, where a model stores them under others.
 
-With any of the first four the layer runs product -> norms + cache write -> attention -> output
+With any of these but the last the layer runs product -> norms + cache write -> attention -> output
 projection with the kernels of those options; scores, softmax and norms are float32.
 """
 
@@ -55,6 +61,8 @@ class Attention(Mixer):
         distance_penalty: bool = False,
         norm_eps: float = 1e-6,
         names: dict[str, str] | None = None,
+        keep_first: int = 0,
+        gate: bool = False,
     ) -> None:
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
@@ -64,6 +72,10 @@ class Attention(Mixer):
         self.head_dim = int(head_dim)
         self.qkv_bias = bool(qkv_bias)
         self.window = int(window)
+        self.keep_first = int(keep_first) if self.window > 0 else 0
+        if keep_first < 0:
+            raise ValueError("keep_first must not be negative")
+        self.gate = bool(gate)
         self.position = build_part("position", position) if position is not None else None
         if getattr(self.position, "magnitude", 1.0) != 1.0 or getattr(self.position, "keep_pairing", False):
             raise ValueError("this mixer's kernels rotate without a magnitude factor and pair (j, j + R/2) only")
@@ -75,21 +87,23 @@ class Attention(Mixer):
         self.v_width = self.num_kv_heads * self.value_dim
         self.out_width = self.num_heads * self.value_dim
         self.qkv_width = self.q_width + self.kv_width + self.v_width
-        if qk_norm not in (None, "projection"):
-            raise ValueError(f"qk_norm must be None or 'projection', got {qk_norm!r}")
+        if qk_norm not in (None, "projection", "head"):
+            raise ValueError(f"qk_norm must be None, 'projection' or 'head', got {qk_norm!r}")
         self.qk_norm = qk_norm
         self.value_norm = bool(value_norm)
         self.distance_penalty = bool(distance_penalty)
         self.norm_eps = float(norm_eps)
         # the options that the rotary kernels and the tensor-core attention kernels do not know
         self.general = bool(self.qk_norm or self.value_norm or self.distance_penalty
-                            or self.value_dim != self.head_dim)
+                            or self.value_dim != self.head_dim or self.keep_first or self.gate)
         if self.general and self.position is not None:
-            raise ValueError("q/k norm, value norm, distance penalty and a value size of its own are built "
-                             "for attention without rotation")
+            raise ValueError("q/k norm, value norm, distance penalty, kept first keys, an output gate and a value "
+                             "size of its own are built for attention without rotation")
+        if self.gate and self.qkv_bias:
+            raise ValueError("the output gate is built for projections without biases")
         self.names = {key: key for key in ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight",
                                            "q_proj.bias", "k_proj.bias", "v_proj.bias", "q_norm", "k_norm",
-                                           "r1", "r2")}
+                                           "r1", "r2", "gate")}
         self.names.update(names or {})
         self.tiled = False      # set at bind: whether prompt portions run on the tensor-core kernel
 
@@ -105,7 +119,8 @@ class Attention(Mixer):
 
     def cache_spec(self) -> CacheSpec:
         return CacheSpec(kv_heads=self.num_kv_heads, head_dim=self.head_dim, window=self.window,
-                         value_dim=0 if self.value_dim == self.head_dim else self.value_dim)
+                         value_dim=0 if self.value_dim == self.head_dim else self.value_dim,
+                         keep_first=self.keep_first)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         n = self.names
@@ -120,8 +135,11 @@ class Attention(Mixer):
             specs[n["k_proj.bias"]] = TensorSpec((self.kv_width,), role="vector")
             specs[n["v_proj.bias"]] = TensorSpec((self.v_width,), role="vector")
         if self.qk_norm:
-            specs[n["q_norm"]] = TensorSpec((self.q_width,), init="gain", role="vector")
-            specs[n["k_norm"]] = TensorSpec((self.kv_width,), init="gain", role="vector")
+            per_head = self.qk_norm == "head"
+            specs[n["q_norm"]] = TensorSpec((self.head_dim if per_head else self.q_width,), init="gain", role="vector")
+            specs[n["k_norm"]] = TensorSpec((self.head_dim if per_head else self.kv_width,), init="gain", role="vector")
+        if self.gate:
+            specs[n["gate"]] = TensorSpec((self.out_width, self.hidden_size))
         if self.distance_penalty:
             specs[n["r1"]] = TensorSpec((self.num_heads,), init="gain", role="vector")
             specs[n["r2"]] = TensorSpec((self.num_heads,), init="gain", role="vector")
@@ -154,6 +172,8 @@ class Attention(Mixer):
             if self.paired:
                 q = ops.pair_rotary_rows(q, self.num_heads, self.head_dim, rotary)
                 k = ops.pair_rotary_rows(k, self.num_kv_heads, self.head_dim, rotary)
+            if self.gate and suffix == "weight":
+                return torch.cat([q, k, v, tensors[self.names["gate"]]]).contiguous()
             return torch.cat([q, k, v]).contiguous()
 
         self.w_qkv = ops.prepare_weight(stacked("weight"))
@@ -167,7 +187,7 @@ class Attention(Mixer):
                          if self.distance_penalty else None)
         # the tensor-core kernels take bfloat16 heads of a multiple of 16 elements, values as large as keys
         self.tiled = bool(self.value_dim == self.head_dim and self.head_dim % 16 == 0 and self.head_dim <= 256
-                          and runtime.dtype_name == "bfloat16")
+                          and runtime.dtype_name == "bfloat16" and not self.keep_first)
         if not self.general or self.tiled:
             runtime.ops.require_attention(self.head_dim)
 
@@ -181,15 +201,19 @@ class Attention(Mixer):
         rt = self.runtime
         tokens = x.shape[0]
         kv = binding.kv
-        qkv = rt.workspace.get("attention.qkv", tokens, self.qkv_width, rt.dtype)
+        width = self.qkv_width + (self.out_width if self.gate else 0)
+        qkv = rt.workspace.get("attention.qkv", tokens, width, rt.dtype)
         qkv = rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv, tag="attention.qkv", defer_bias=True)
         q = rt.workspace.get("attention.q", tokens, self.q_width, rt.dtype)
         rt.ops.norm_kv_write(qkv, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim,
                              self.q_gain, self.k_gain, self.value_norm, self.norm_eps, q,
-                             write_cache=binding.owns_cache)
+                             write_cache=binding.owns_cache, per_head=self.qk_norm == "head")
         mixed = rt.workspace.get("attention.out", tokens, self.out_width, rt.dtype)
         rt.ops.attention_penalised(q, mixed, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim,
-                                   self.value_dim, self.scale, self.window, self.distance)
+                                   self.value_dim, self.scale, self.window, self.distance,
+                                   keep_first=self.keep_first)
+        if self.gate:
+            rt.ops.sigmoid_gate(mixed, qkv[:, self.qkv_width:])
         update = rt.workspace.get("mixer.update32", tokens, self.hidden_size, torch.float32)
         return rt.ops.linear(mixed, self.w_o, None, update)
 

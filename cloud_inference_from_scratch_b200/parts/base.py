@@ -52,12 +52,14 @@ class TensorSpec:
 class CacheSpec:
     """What a mixer needs of the page manager: keys and values for ``kv_heads`` heads of
     ``head_dim`` per token, for all earlier tokens (``window == 0``) or the last ``window``.
-    ``value_dim`` is the size of a value head where it differs from that of a key head (0: the same)."""
+    ``value_dim`` is the size of a value head where it differs from that of a key head (0: the same).
+    ``keep_first``: with a window, the request's first so many tokens stay readable behind it."""
 
     kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: int = 0
+    keep_first: int = 0
 
     @property
     def value_size(self) -> int:
@@ -65,9 +67,11 @@ class CacheSpec:
 
     @property
     def group_key(self) -> tuple[int, ...]:
-        if self.value_size == self.head_dim:
+        if self.value_size == self.head_dim and not self.keep_first:
             return (self.window, self.kv_heads, self.head_dim)
-        return (self.window, self.kv_heads, self.head_dim, self.value_size)
+        if not self.keep_first:
+            return (self.window, self.kv_heads, self.head_dim, self.value_size)
+        return (self.window, self.kv_heads, self.head_dim, self.value_size, self.keep_first if self.window else 0)
 
 
 @dataclass(frozen=True)
@@ -92,6 +96,11 @@ class Part:
 
     def bind(self, tensors: dict[str, "torch.Tensor"], runtime: "Runtime") -> None:
         self.runtime = runtime
+
+    def subparts(self) -> "tuple[Part, ...]":
+        """Parts this part is put together from (a mixer made of two mixers names them here), for whoever walks
+        all parts of a model: the step function looking for planners, for instance."""
+        return ()
 
 
 class Norm(Part):

@@ -27,8 +27,16 @@ def _lazy_gain(norm, consumer):
 
 
 class PreNormResidual(Block):
-    slots = ("mixer", "feed_forward", "mixer_norm", "feed_forward_norm")
+    """``feed_forward`` and ``feed_forward_norm`` may both be left out: the layer is then its mixer sublayer alone."""
+
+    slots = ("mixer", "mixer_norm")
     kernels_through_ops = True   # the block itself launches nothing
+
+    def __init__(self, parts, **params) -> None:
+        super().__init__(parts, **params)
+        if ("feed_forward" in parts) != ("feed_forward_norm" in parts):
+            raise ValueError("PreNormResidual: a feed-forward and its norm come together or not at all")
+        self.has_feed_forward = "feed_forward" in parts
 
     def entry_gain(self):
         return _lazy_gain(self.mixer_norm, self.mixer)
@@ -41,6 +49,10 @@ class PreNormResidual(Block):
             # weights only, so the projection may let them start early
             sink.early_trigger = True
         x = _normalise(self.mixer_norm, self.mixer, residual, pending, ctx)
+        if not self.has_feed_forward:
+            if sink is not None:   # the mixer's sum is read next by whoever comes after this layer
+                sink.gain = sink.following_gain
+            return self.mixer.forward(x, ctx, binding)
         if sink is not None:   # the mixer's sum is read next by this layer's second norm
             sink.gain = _lazy_gain(self.feed_forward_norm, self.feed_forward)
         update = self.mixer.forward(x, ctx, binding)

@@ -91,3 +91,40 @@ class ClampedGLU(FeedForward):
 
 
 register_part("feed_forward", "clamped_glu", ClampedGLU, replace=True)
+
+
+class DenseActivation(FeedForward):
+    """Feed-forward without a gate: ``W_down act(W_up x)``, no biases.  ``activation`` "relu2": the square of
+    relu.  The up product has float32 results, the activation runs in float32 and is rounded once; the result
+    is float32 (a term of the residual sum).  Tensor names: ``up``, ``down``."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "relu2") -> None:
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        if activation not in ("relu2",):
+            raise ValueError(f"dense feed-forward: activation {activation!r} is not built (known: relu2)")
+        self.activation = activation
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        return {"up": TensorSpec((self.intermediate_size, self.hidden_size)),
+                "down": TensorSpec((self.hidden_size, self.intermediate_size))}
+
+    def bind(self, tensors, runtime) -> None:
+        self.runtime = runtime
+        self.w_up = runtime.ops.prepare_weight(tensors["up"])
+        self.w_down = runtime.ops.prepare_weight(tensors["down"])
+
+    def forward(self, x, ctx):
+        import torch
+
+        rt = self.runtime
+        tokens = x.shape[0]
+        raised = rt.workspace.get("dense.up", tokens, self.intermediate_size, torch.float32)
+        rt.ops.linear(x, self.w_up, None, raised)
+        hidden = rt.workspace.get("dense.hidden", tokens, self.intermediate_size, rt.dtype)
+        rt.ops.unary_act(raised, hidden, self.activation)
+        update = rt.workspace.get("feed_forward.update32", tokens, self.hidden_size, torch.float32)
+        return rt.ops.linear(hidden, self.w_down, None, update)
+
+
+register_part("feed_forward", "dense_activation", DenseActivation, replace=True)
