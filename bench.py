@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl own|reference]
-                    [--config 3b|7b-mixed|14b-pressure|zisesun|lodalix] [--quick]
+                    [--config 3b|7b-mixed|14b-pressure|zisesun|lodalix|lazilorn] [--quick]
 
 Prints ONE JSON line.  The default configuration is the Qwen2.5-3B shape: a "step" is one decode
 step of a batch of requests whose prompts (2,048 random tokens each) were prefilled before;
@@ -31,6 +31,11 @@ of 256 and 512 tokens, and (unless ``--quick``) the two other benchmark configur
   rotary frequencies, layers that read an earlier layer's latent, the generalized delta rule, a
   clamped gated feed-forward beside the mixer) at two sizes, beside the Qwen2 dense shape of equal
   width, layer count, head count and feed-forward size, measured the same way.
+
+* ``lazilorn``: the Lazilorn design (windowed attention that keeps the first keys, with per-head q/k norm
+  and an output gate, beside a matrix memory; the gated delta rule with short convolutions; a squared-relu
+  feed-forward; looped layers) at two sizes, beside the Qwen2 dense shape of equal width, layer runs, head
+  count and feed-forward size and beside the Zisesun configuration of that size, measured the same way.
 
 ``check`` compares, at the full 36 layers, the logits of the bfloat16 generation path with the
 32-bit path of the same weights (``engine/check.py``).  ``--config`` prints the line of one of the
@@ -612,6 +617,33 @@ LODALIX_SIZES = {
 }
 
 
+def _lazilorn(width, layers, loop, heads, kv_heads, dim, window, keep, memory_heads, delta_heads, delta_kv_heads, ff,
+              vocab=32000) -> dict:
+    """``layers``: a string of P (windowed attention beside a matrix memory, with feed-forward) and D (gated
+    delta rule, with feed-forward); ``loop``: (start, stop, times) or None."""
+    left = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, mask=dict(size=window, keep_first=keep))
+    right = dict(heads=memory_heads, dim=dim, vdim=dim, gate_cap=15.0)
+    mlp = dict(kind="dense", ff=ff)
+    kinds = {"P": dict(type="parallel", mixer=dict(left=left, right=right, left_scale=1.0, right_scale=1.0), mlp=mlp),
+             "D": dict(type="delta", mixer=dict(heads=delta_heads, kv_heads=delta_kv_heads, dim=dim, vdim=dim, conv=4), mlp=mlp)}
+    raw = dict(architecture="Lazilorn", vocab=vocab, width=width, norm=dict(eps=1e-6), embedding=dict(scale=1.0),
+               logit_scale=1.0, layers=[kinds[letter] for letter in layers])
+    if loop is not None:
+        raw["loop"] = dict(start=loop[0], stop=loop[1], times=loop[2])
+    return raw
+
+
+# (Lazilorn configuration, the Qwen2 dense shape of equal width, layer runs, heads and feed-forward size, and the
+# Zisesun configuration of that size: the design whose mixers are nearest, windowed attention without rotation and
+# a float32 matrix recurrence).  w2048: six layers of which two run twice (eight layer runs: P PD PD P P D).
+LAZILORN_SIZES = {
+    "w2048": (_lazilorn(2048, "PPDPPD", (1, 3, 2), 16, 2, 128, 1024, 4, 8, 16, 8, 5504),
+              dict(_qwen2(2048, 8, 16, 2, 5504, 32000, False)), ZISESUN_SIZES["w2048"][0]),
+    "w4096": (_lazilorn(4096, "PD", (0, 2, 2), 32, 8, 128, 1024, 4, 16, 32, 16, 8192),
+              dict(_qwen2(4096, 4, 32, 8, 8192, 32000, False)), ZISESUN_SIZES["w4096"][0]),
+}
+
+
 def _time_step_function(cfg: dict, batch: int, steps: int, warmup: int, only: str = "all") -> dict:
     """Prefill of one PROMPT_TOKENS prompt in one step (median of 5 after 3), then ``steps`` decode
     steps of ``batch`` requests that each hold a PROMPT_TOKENS context, through the step function;
@@ -683,7 +715,7 @@ def run_design(args: argparse.Namespace, design: str = "zisesun") -> int:
     """A second or third design at its sizes beside the Qwen2 dense shape of equal size."""
     import torch
 
-    sizes = {"zisesun": ZISESUN_SIZES, "lodalix": LODALIX_SIZES}[design]
+    sizes = {"zisesun": ZISESUN_SIZES, "lodalix": LODALIX_SIZES, "lazilorn": LAZILORN_SIZES}[design]
     title = design.capitalize()
 
     if not torch.cuda.is_available():
@@ -692,9 +724,12 @@ def run_design(args: argparse.Namespace, design: str = "zisesun") -> int:
     sampler = ClockSampler()
     sampler.start()
     points = {}
-    for name, (zisesun, qwen) in sizes.items():
+    for name, (zisesun, qwen, *nearest) in sizes.items():
         if args.size not in ("all", name):
             continue
+        if args.layers and design == "lazilorn":
+            print("bench.py: --layers does not go with --config lazilorn (its layer runs come from a loop)")
+            return 2
         if args.layers:
             zisesun = dict(zisesun, layers=zisesun["layers"][:args.layers])
             qwen = dict(qwen, num_hidden_layers=args.layers)
@@ -703,9 +738,11 @@ def run_design(args: argparse.Namespace, design: str = "zisesun") -> int:
             points[name][design] = _time_step_function(zisesun, args.batch, args.steps, args.warmup, args.only)
         if args.model in ("both", "qwen2"):
             points[name]["qwen2_dense"] = _time_step_function(qwen, args.batch, args.steps, args.warmup, args.only)
+        if nearest and args.model in ("both", "zisesun"):
+            points[name]["zisesun"] = _time_step_function(nearest[0], args.batch, args.steps, args.warmup, args.only)
         points[name]["layers"] = len(zisesun["layers"])
     first = next(iter(points.values()))
-    main = first.get(design) or first["qwen2_dense"]
+    main = first.get(design) or first.get("qwen2_dense") or first["zisesun"]
     line = {"metric": f"decode tok/s, {title} design at width 2,048 (8 requests at context 2,048), step function",
             "value": main["decode_tokens_per_s"], "unit": "tokens/s", "higher_is_better": True,
             "ms_per_step": main["decode_ms_per_step"], "steps": args.steps, "n_gpus": 1, "warmup": args.warmup,
@@ -752,9 +789,10 @@ def main() -> int:
                              "default is 2048; longer ones are for profiles of long contexts, own arm only)")
     parser.add_argument("--impl", default="own", choices=("own", "reference"))
     parser.add_argument("--size", default="all", help="--config zisesun or lodalix: one of its sizes (w2048, w4096)")
-    parser.add_argument("--model", default="both", choices=("both", "zisesun", "lodalix", "qwen2"),
-                        help="--config zisesun or lodalix: only the new design, or only its dense peer")
-    parser.add_argument("--config", default="3b", choices=("3b", "7b-mixed", "14b-pressure", "zisesun", "lodalix"),
+    parser.add_argument("--model", default="both", choices=("both", "zisesun", "lodalix", "lazilorn", "qwen2"),
+                        help="--config zisesun, lodalix or lazilorn: only that design, or only its dense peer "
+                             "(--config lazilorn --model zisesun: only the Zisesun configuration of that size)")
+    parser.add_argument("--config", default="3b", choices=("3b", "7b-mixed", "14b-pressure", "zisesun", "lodalix", "lazilorn"),
                         help="the benchmark configuration whose line is printed (default: the 3B line, "
                              "which also carries the other two as points)")
     parser.add_argument("--quick", action="store_true",
@@ -778,7 +816,7 @@ def main() -> int:
         CONTEXT = min(limit, PROMPT_TOKENS + max(2048, room))
     if args.impl == "reference":
         return run_reference(args)
-    if args.config in ("zisesun", "lodalix"):
+    if args.config in ("zisesun", "lodalix", "lazilorn"):
         return run_design(args, args.config)
     if args.config != "3b":
         return run_other_config(args)

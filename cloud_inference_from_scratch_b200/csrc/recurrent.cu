@@ -34,6 +34,7 @@ namespace cie {
 constexpr int kLanes = 8;        // lanes that share a value column
 constexpr int kScanMaxDim = 256;  // largest number of rows (key size) of a state matrix
 constexpr int kMaxTaps = 16;     // longest short convolution
+constexpr int kNormaliserColumns = 32;   // value columns that share one copy of the matrix memory's n and m
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
@@ -48,8 +49,11 @@ __device__ __forceinline__ float lanes_sum(float v) {
 
 // ---------------------------------------------------------------- matrix memory
 // proj: float32 rows; q, k (heads x dim), v (heads x vdim) and the two gate projections (heads) start at the
-// given columns.  state: per slot `state_stride` floats; per head [S: dim * vdim][n: dim][m: 1].
-// R = rows of a lane, C = value columns of a block.
+// given columns.  state: per slot `state_stride` floats; per head [S: dim * vdim] and then, once for every
+// kNormaliserColumns value columns, [n: dim][m: 1].  n and m do not depend on the column; every block keeps
+// them for its own columns and reads and writes only the copies of its columns, so that no block reads what
+// another block of the same launch has written.  R = rows of a lane, C = value columns of a block (a multiple
+// of kNormaliserColumns).
 template <int R, int C>
 __global__ void __launch_bounds__(kLanes * C)
 mlstm_scan_kernel(const float* __restrict__ proj, int proj_stride, int q_off, int k_off, int v_off, int i_off,
@@ -70,8 +74,12 @@ mlstm_scan_kernel(const float* __restrict__ proj, int proj_stride, int q_off, in
     return;
   }
   const int begin = query_start[request], end = query_start[request + 1];
-  float* s_base = state + (size_t)slot * state_stride + (size_t)head * ((size_t)dim * vdim + dim + 1);
-  float* n_base = s_base + (size_t)dim * vdim;
+  static_assert(C % kNormaliserColumns == 0, "a block owns whole copies of n and m");
+  const int copies = (vdim + kNormaliserColumns - 1) / kNormaliserColumns;
+  const int first_copy = blockIdx.z * (C / kNormaliserColumns);
+  const int last_copy = min(first_copy + C / kNormaliserColumns, copies);
+  float* s_base = state + (size_t)slot * state_stride + (size_t)head * ((size_t)dim * vdim + (size_t)copies * (dim + 1));
+  float* n_base = s_base + (size_t)dim * vdim + (size_t)first_copy * (dim + 1);
   float s[R], n[R];
 #pragma unroll
   for (int i = 0; i < R; ++i) {
@@ -137,9 +145,11 @@ mlstm_scan_kernel(const float* __restrict__ proj, int proj_stride, int q_off, in
     const int row = part * R + i;
     if (row >= dim) continue;
     if (live) s_base[(size_t)row * vdim + column] = s[i];
-    if (blockIdx.z == 0 && tid < kLanes) n_base[row] = n[i];
+    if (tid < kLanes)
+      for (int copy = first_copy; copy < last_copy; ++copy) n_base[(size_t)(copy - first_copy) * (dim + 1) + row] = n[i];
   }
-  if (blockIdx.z == 0 && tid == 0) n_base[dim] = m;
+  if (tid == 0)
+    for (int copy = first_copy; copy < last_copy; ++copy) n_base[(size_t)(copy - first_copy) * (dim + 1) + dim] = m;
 }
 
 // ---------------------------------------------------------------- short convolution + SiLU
@@ -332,6 +342,7 @@ using namespace cie;
 
 extern "C" int cie_scan_max_dim() { return kScanMaxDim; }
 extern "C" int cie_conv_max_taps() { return kMaxTaps; }
+extern "C" int cie_normaliser_columns() { return kNormaliserColumns; }
 
 // Chooses the rows of a lane and the columns of a block from the sizes and runs BODY(R, C).
 #define CIE_SCAN_SHAPES(name, dim, vdim, BODY)                                                           \

@@ -383,6 +383,7 @@ class Ops:
             self._head_norm_gate = lib.function("cie_head_norm_gate", [v, i, v, i, v, i, i, v, i, i, i, i, f, i, v])
             self.scan_max_dim = int(lib.handle.cie_scan_max_dim())
             self.conv_max_taps = int(lib.handle.cie_conv_max_taps())
+            self.normaliser_columns = int(lib.handle.cie_normaliser_columns())
             self._recurrent_lib = lib
 
     def require_recurrent(self) -> tuple[int, int]:
@@ -394,8 +395,8 @@ class Ops:
     def mlstm_scan(self, proj: Any, offsets: tuple[int, int, int, int, int], input_bias: Any, forget_bias: Any,
                    cap: float, q_scale: float, out: Any, state: Any, ctx: Any, heads: int, dim: int, vdim: int) -> None:
         """Runs the matrix memory (mLSTM) over every request's new tokens from the state in its slot
-        (``state``: float32 [slots, heads * (dim * vdim + dim + 1)]: per head the matrix, the normaliser and
-        the running maximum).  ``proj`` float32 rows hold q, k, v and the two gate projections from the
+        (``state``: float32 [slots, heads * (dim * vdim + copies * (dim + 1))]: per head the matrix and then
+        the normaliser and the running maximum, once for every ``normaliser_columns`` value columns).  ``proj`` float32 rows hold q, k, v and the two gate projections from the
         columns ``offsets``; ``out`` float32 [T, heads * vdim]."""
         self._flush()
         self._load_recurrent()

@@ -25,6 +25,9 @@ from __future__ import annotations
 from .base import Mixer, StateSpec, TensorSpec, register_part
 
 
+NORMALISER_COLUMNS = 32     # as the scan kernel lays a head's state out
+
+
 class MatrixMemory(Mixer):
     state_in_graphs = True   # the scan reads the step's numbers on the device and honours request_active
 
@@ -44,8 +47,10 @@ class MatrixMemory(Mixer):
         self.names.update(names or {})
 
     def state_spec(self) -> StateSpec:
-        # per head: the matrix, the normaliser vector, the running maximum
-        return StateSpec((self.num_heads * (self.key_dim * self.value_dim + self.key_dim + 1),), "float32")
+        # per head: the matrix, then the normaliser vector and the running maximum once for every
+        # NORMALISER_COLUMNS value columns (the blocks of a scan share no word that one of them writes)
+        copies = -(-self.value_dim // NORMALISER_COLUMNS)
+        return StateSpec((self.num_heads * (self.key_dim * self.value_dim + copies * (self.key_dim + 1)),), "float32")
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         n, hidden = self.names, self.hidden_size
@@ -64,6 +69,8 @@ class MatrixMemory(Mixer):
         self.runtime = runtime
         ops, n = runtime.ops, self.names
         largest, _ = ops.require_recurrent()
+        if ops.normaliser_columns != NORMALISER_COLUMNS:
+            raise RuntimeError("the scan kernel and this part disagree on the layout of a head's state")
         if self.key_dim > largest:
             raise ValueError(f"the scan kernels take key sizes of up to {largest}, got {self.key_dim}")
         self.w_in = ops.prepare_weight(torch.cat([tensors[n[key]] for key in ("q", "k", "v", "g", "i", "f")]))
