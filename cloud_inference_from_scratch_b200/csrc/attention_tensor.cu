@@ -56,6 +56,7 @@ struct PrefillArgs {
   int head_chunks;   // ceil(group / hpt)
   float scale_log2;
   int window;
+  int keep_first;    // with a window: the request's first so many keys stay visible behind it
   int* err;
   // a penalty that grows with the distance between query and key, per query head: the score (in
   // units of log 2) is lowered by r1[h] * log2(1 + r2[h] * (position - key)); nullptr: none
@@ -66,17 +67,21 @@ struct PrefillArgs {
 
 // One 64-key tile: thread t < 64 copies key row t of K, thread 64 + t row t of V, each with one bulk
 // asynchronous copy of a whole row (a row never crosses a page, so any page size works).  Rows
-// outside [valid_lo, valid_hi) are not copied.  Thread 0 arms the stage's mbarrier.
+// outside [valid_lo, valid_hi) and not below `kept` (<= valid_lo: the first keys that stay visible behind
+// a window) are not copied.  Thread 0 arms the stage's mbarrier.
+__device__ __forceinline__ int kv_tile_rows(int k0, int valid_lo, int valid_hi, int kept) {
+  return max(0, min(k0 + BN, valid_hi) - max(k0, valid_lo)) + max(0, min(k0 + BN, kept) - k0);
+}
+
 __device__ __forceinline__ void load_kv_tile(const PrefillArgs& a, const int* row, int kvh, int k0,
-                                             int valid_lo, int valid_hi, bf16* k_dst, bf16* v_dst,
+                                             int valid_lo, int valid_hi, int kept, bf16* k_dst, bf16* v_dst,
                                              uint64_t* bar, int tid) {
-  const int lo = max(k0, valid_lo), hi = min(k0 + BN, valid_hi);
-  const int rows = max(0, hi - lo);
+  const int rows = kv_tile_rows(k0, valid_lo, valid_hi, kept);
   if (tid == 0) mbar_expect_tx(bar, (uint32_t)rows * 2u * ROW_BYTES);
   if (tid >= 2 * BN) return;
   const int r = tid & (BN - 1);
   const int key = k0 + r;
-  if (key < lo || key >= hi) return;
+  if (key >= valid_hi || (key < valid_lo && key >= kept)) return;
   long long off = kv_offset(a.pools, row, key, kvh, a.err);
   if (off < 0) off = (long long)kvh * a.pools.page_size * D;   // page 0: the copy must still happen
   if (tid < BN) bulk_copy(k_dst + r * ROW, a.pools.k + off, ROW_BYTES, bar);
@@ -113,13 +118,18 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
   const int valid_lo = a.window > 0 ? max(0, pos_lo - a.window + 1) : 0;
   const int valid_hi = pos_hi + 1;
   const int k_begin = (valid_lo / BN) * BN;
-  const int tiles = (valid_hi - k_begin + BN - 1) / BN;
+  // kept first keys below the window's range: whole tiles from key 0 come first (a tile that the kept keys
+  // share with the window's range is taken once, with the window's)
+  const int kept = min(a.keep_first, valid_lo);
+  const int pre = min((kept + BN - 1) / BN, k_begin / BN);
+  const int tiles = pre + (valid_hi - k_begin + BN - 1) / BN;
+  auto tile_k0 = [&](int it) { return it < pre ? it * BN : k_begin + (it - pre) * BN; };
 
   __shared__ __align__(8) uint64_t bars[2];
   if (tid < 2) mbar_init(&bars[tid], 1);
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   __syncthreads();
-  load_kv_tile(a, table_row, kvh, k_begin, valid_lo, valid_hi, k_s, v_s, &bars[0], tid);
+  load_kv_tile(a, table_row, kvh, tile_k0(0), valid_lo, valid_hi, kept, k_s, v_s, &bars[0], tid);
 
   uint32_t q_frag[KSTEPS][4];
   float o[NTILES_D][4];
@@ -146,19 +156,19 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
   for (int it = 0; it < tiles && alive; ++it) {
     const int stage = it & 1;
     if (it + 1 < tiles)
-      load_kv_tile(a, table_row, kvh, k_begin + (it + 1) * BN, valid_lo, valid_hi,
+      load_kv_tile(a, table_row, kvh, tile_k0(it + 1), valid_lo, valid_hi, kept,
                    k_s + (stage ^ 1) * BN * ROW, v_s + (stage ^ 1) * BN * ROW, &bars[stage ^ 1], tid);
     if (it == 0) cp_async_wait<0>();   // the queries
     alive = mbar_wait(&bars[stage], (it >> 1) & 1, a.err);
-    const int k0 = k_begin + it * BN;
+    const int k0 = tile_k0(it);
     {
       // rows of this tile that were not copied: their V must not hold NaN or Inf bits
-      const int lo = max(k0, valid_lo), hi = min(k0 + BN, valid_hi);
-      if (hi - lo < BN) {
+      if (kv_tile_rows(k0, valid_lo, valid_hi, kept) < BN) {
         bf16* v_tile = v_s + stage * BN * ROW;
         for (int e = tid; e < BN * (D / 2); e += PREFILL_WARPS * 32) {
           const int r = e / (D / 2), c = e % (D / 2);
-          if (k0 + r < lo || k0 + r >= hi) reinterpret_cast<uint32_t*>(v_tile + r * ROW)[c] = 0u;
+          const int key = k0 + r;
+          if (key >= valid_hi || (key < valid_lo && key >= kept)) reinterpret_cast<uint32_t*>(v_tile + r * ROW)[c] = 0u;
         }
         // these ordinary stores must be ordered before later bulk copies into the same stage
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -181,7 +191,7 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
         for (int e = 0; e < 4; ++e) {
           const int key = k0 + i * 8 + 2 * t4 + (e & 1);
           const int pos = row_pos[e >> 1];
-          const bool ok = key <= pos && (a.window <= 0 || key > pos - a.window);
+          const bool ok = key <= pos && (a.window <= 0 || key > pos - a.window || key < a.keep_first);
           float score = s[i][e] * a.scale_log2;
           if (a.r1 && ok) score -= row_r1[e >> 1] * __log2f(fmaf(row_r2[e >> 1], (float)(pos - key), 1.f));
           s[i][e] = ok ? score : -INFINITY;
@@ -1135,16 +1145,18 @@ static const float kLog2e = 1.4426950408889634f;
 extern "C" int cie_attention_head_dim() { return D; }
 
 // r1, r2: float32 [q_heads] of the distance penalty, or both null; split_weights: 1 keeps the
-// softmax weights to 16 bits of mantissa in the value product (two bfloat16 terms).
+// softmax weights to 16 bits of mantissa in the value product (two bfloat16 terms); keep_first: with a window,
+// the request's first so many keys stay visible behind it.
 extern "C" int cie_attention_prefill_ex(const void* q, int q_stride, void* out, int out_stride,
                                         const void* k_pool, const void* v_pool, const int* table,
                                         int table_width, int num_pages, const int* tile_request,
                                         const int* tile_q0, int num_tiles, const int* context_lens,
                                         const int* query_lens, const int* query_start, int q_heads,
                                         int kv_heads, int page_size, int hpt, float scale, int window,
-                                        const float* r1, const float* r2, int split_weights,
+                                        const float* r1, const float* r2, int split_weights, int keep_first,
                                         int* err, void* stream) {
   if (num_tiles <= 0) return 0;
+  if (keep_first < 0) CIE_FAIL("attention_prefill: %d kept first keys", keep_first);
   if ((r1 == nullptr) != (r2 == nullptr)) CIE_FAIL("attention_prefill: the distance penalty needs both of its vectors");
   if (kv_heads < 1 || q_heads % kv_heads) CIE_FAIL("attention_prefill: %d query heads over %d kv heads", q_heads, kv_heads);
   const int group = q_heads / kv_heads;
@@ -1156,7 +1168,7 @@ extern "C" int cie_attention_prefill_ex(const void* q, int q_stride, void* out, 
   a.tile_request = tile_request; a.tile_q0 = tile_q0; a.context_lens = context_lens;
   a.query_lens = query_lens; a.query_start = query_start;
   a.group = group; a.hpt = hpt; a.tpt = BM / hpt; a.head_chunks = (group + hpt - 1) / hpt;
-  a.scale_log2 = scale * kLog2e; a.window = window; a.err = err;
+  a.scale_log2 = scale * kLog2e; a.window = window; a.keep_first = window > 0 ? keep_first : 0; a.err = err;
   a.r1 = r1; a.r2 = r2; a.split_weights = split_weights;
   const size_t smem = (size_t)(BM + 4 * BN) * ROW * sizeof(bf16);
   static bool configured = false;
@@ -1179,7 +1191,7 @@ extern "C" int cie_attention_prefill(const void* q, int q_stride, void* out, int
                                      int* err, void* stream) {
   return cie_attention_prefill_ex(q, q_stride, out, out_stride, k_pool, v_pool, table, table_width, num_pages,
                                   tile_request, tile_q0, num_tiles, context_lens, query_lens, query_start,
-                                  q_heads, kv_heads, page_size, hpt, scale, window, nullptr, nullptr, 0, err,
+                                  q_heads, kv_heads, page_size, hpt, scale, window, nullptr, nullptr, 0, 0, err,
                                   stream);
 }
 

