@@ -569,6 +569,331 @@ recurrent_stream_kernel(const float* __restrict__ packed, float* __restrict__ ou
   }
 }
 
+// ---------------------------------------------------------------- matrix memory over prompt portions, in chunks
+// The matrix memory's state is a sum over earlier tokens with weights that are products of scalars, so a
+// prompt portion can be cut into chunks of kMemChunk tokens that many CTAs work on at once.  With b_t the log
+// forget gates summed from the chunk's first token to t, m_t the running maximum (the recurrence above, taken
+// token by token so that it is the same number in every form) and m_c the maximum before the chunk:
+//   1. per (request, head), one warp:   the gates of every token: i_t, b_t, m_t, m_(t-1)
+//   2. per (chunk, head):               U = sum_s exp(b_last - b_s + i_s - m_last) k_s v_s^T, and the same with k_s alone
+//   3. per (request, head):             walks its chunks, S <- exp(b_last + m_c - m_last) S + U, leaving in U's place
+//                                       the state BEFORE the chunk; the last S, n and m go back to the slot
+//   4. per (chunk, head):               o_t = (exp(b_t + m_c - m_t) S_c^T q_t + sum_(s<=t) a_ts v_s) / (max(|nq_t|, exp(-m_t)) + 1e-6),
+//                                       a_ts = exp(b_t - b_s + i_s - m_t) (q_t . k_s),
+//                                       nq_t = exp(b_t + m_c - m_t) (n_c . q_t) + sum_(s<=t) a_ts
+// No exponent is above zero (m_t is at least every one of them), all float32 on the CUDA cores; key and value
+// sizes up to kMemDim.  Chunks come as a work list made on the host; a request's chunks follow each other and
+// start at multiples of kMemChunk tokens from the portion's first token.
+constexpr int kMemChunk = 32;
+constexpr int kMemWarps = 8;
+constexpr int kMemDim = 128;                     // largest key and value size
+constexpr int kMemRows = kMemDim / kMemWarps;    // state rows of a warp
+constexpr int kMemCols = kMemDim / 32;           // value columns of a lane
+constexpr int kMemGates = 4;                     // floats per token and head: i_t, b_t, m_t, m_(t-1)
+
+// grid (requests, heads); one warp
+__global__ void __launch_bounds__(32)
+mlstm_gate_walk_kernel(const float* __restrict__ proj, int proj_stride, int i_off, int f_off,
+                       const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
+                       const float* __restrict__ state, long long state_stride, float* __restrict__ gates,
+                       const int* __restrict__ query_start, const int* __restrict__ slots, int heads, int dim, int vdim,
+                       int max_slots, int* err) {
+  pdl_wait();
+  pdl_trigger();
+  const int request = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  const int slot = slots[request];
+  if (slot < 0 || slot >= max_slots) {
+    if (lane == 0) atomicOr(err, kErrBadRequest);
+    return;
+  }
+  const int begin = query_start[request], end = query_start[request + 1];
+  const int copies = (vdim + kNormaliserColumns - 1) / kNormaliserColumns;
+  const size_t head_floats = (size_t)dim * vdim + (size_t)copies * (dim + 1);
+  float m = state[(size_t)slot * state_stride + (size_t)head * head_floats + (size_t)dim * vdim + dim];
+  const float bi = i_bias[head], bf = f_bias[head];
+  for (int t0 = begin; t0 < end; t0 += kMemChunk) {
+    const int t = t0 + lane, n = min(kMemChunk, end - t0);
+    float gi = 0.f, gf = 0.f;
+    if (t < end) {
+      const float* row = proj + (size_t)t * proj_stride;
+      gi = cap * tanhf((row[i_off + head] + bi) / cap);
+      gf = log_sigmoid_f(cap * tanhf((row[f_off + head] + bf) / cap));
+    }
+    float b = 0.f, my_b = 0.f, my_m = 0.f, my_before = 0.f;
+    for (int j = 0; j < n; ++j) {
+      const float fj = __shfl_sync(0xffffffffu, gf, j), ij = __shfl_sync(0xffffffffu, gi, j);
+      b += fj;
+      const float m_new = fmaxf(fj + m, ij);
+      if (lane == j) {
+        my_b = b;
+        my_before = m;
+        my_m = m_new;
+      }
+      m = m_new;
+    }
+    if (t < end)
+      *reinterpret_cast<float4*>(gates + ((size_t)t * heads + head) * kMemGates) = make_float4(gi, my_b, my_m, my_before);
+  }
+}
+
+// dst[j * ld + i] = proj[row0 + j][col0 + i] * factor(j) for j < n, i < width: 16-byte loads where the columns allow
+template <typename Factor>
+__device__ __forceinline__ void stage_rows(float* __restrict__ dst, int ld, const float* __restrict__ proj, int proj_stride,
+                                           int row0, int n, int col0, int width, Factor factor) {
+  if (width % 4 == 0 && col0 % 4 == 0 && proj_stride % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0) {
+    const int pieces = width / 4;
+    for (int e = threadIdx.x; e < n * pieces; e += blockDim.x) {
+      const int j = e / pieces, i = (e % pieces) * 4;
+      float4 x = *reinterpret_cast<const float4*>(proj + (size_t)(row0 + j) * proj_stride + col0 + i);
+      const float f = factor(j);
+      x.x *= f; x.y *= f; x.z *= f; x.w *= f;
+      *reinterpret_cast<float4*>(dst + j * ld + i) = x;
+    }
+    return;
+  }
+  for (int e = threadIdx.x; e < n * width; e += blockDim.x) {
+    const int j = e / width, i = e % width;
+    dst[j * ld + i] = proj[(size_t)(row0 + j) * proj_stride + col0 + i] * factor(j);
+  }
+}
+
+// grid (chunks, heads).  chunk_sums: per chunk and head [U: dim * vdim][the same with k alone: dim]
+__global__ void __launch_bounds__(kMemWarps * 32)
+mlstm_chunk_sums_kernel(const float* __restrict__ proj, int proj_stride, int k_off, int v_off,
+                        const float* __restrict__ gates, float* __restrict__ chunk_sums,
+                        const int* __restrict__ chunk_row, const int* __restrict__ chunk_count, int heads, int dim, int vdim) {
+  extern __shared__ __align__(16) float smem[];
+  float* k_s = smem;                        // [kMemChunk][dim], times the token's weight
+  float* v_s = smem + kMemChunk * dim;      // [kMemChunk][vdim]
+  __shared__ float w_s[kMemChunk];
+  pdl_wait();
+  pdl_trigger();
+  const int chunk = blockIdx.x, head = blockIdx.y;
+  const int row0 = chunk_row[chunk], n = chunk_count[chunk];
+  if (threadIdx.x < n) {
+    const float4 g = *reinterpret_cast<const float4*>(gates + ((size_t)(row0 + threadIdx.x) * heads + head) * kMemGates);
+    const float4 last = *reinterpret_cast<const float4*>(gates + ((size_t)(row0 + n - 1) * heads + head) * kMemGates);
+    w_s[threadIdx.x] = expf(last.y - g.y + g.x - last.z);
+  }
+  __syncthreads();
+  stage_rows(k_s, dim, proj, proj_stride, row0, n, k_off + head * dim, dim, [&](int j) { return w_s[j]; });
+  stage_rows(v_s, vdim, proj, proj_stride, row0, n, v_off + head * vdim, vdim, [](int) { return 1.f; });
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int i0 = warp * kMemRows;
+  const bool whole = dim % 4 == 0 && i0 + kMemRows <= dim;
+  float u[kMemRows][kMemCols] = {};
+  for (int j = 0; j < n; ++j) {
+    float vv[kMemCols], kv[kMemRows];
+#pragma unroll
+    for (int c = 0; c < kMemCols; ++c) vv[c] = lane + 32 * c < vdim ? v_s[j * vdim + lane + 32 * c] : 0.f;
+    if (whole) {
+#pragma unroll
+      for (int r = 0; r < kMemRows; r += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(k_s + j * dim + i0 + r);
+        kv[r] = k4.x; kv[r + 1] = k4.y; kv[r + 2] = k4.z; kv[r + 3] = k4.w;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < kMemRows; ++r) kv[r] = i0 + r < dim ? k_s[j * dim + i0 + r] : 0.f;
+    }
+#pragma unroll
+    for (int r = 0; r < kMemRows; ++r)
+#pragma unroll
+      for (int c = 0; c < kMemCols; ++c) u[r][c] = fmaf(kv[r], vv[c], u[r][c]);
+  }
+  float* dst = chunk_sums + ((size_t)chunk * heads + head) * ((size_t)dim * vdim + dim);
+#pragma unroll
+  for (int r = 0; r < kMemRows; ++r) {
+    const int i = i0 + r;
+    if (i >= dim) continue;
+#pragma unroll
+    for (int c = 0; c < kMemCols; ++c)
+      if (lane + 32 * c < vdim) dst[(size_t)i * vdim + lane + 32 * c] = u[r][c];
+  }
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float total = 0.f;
+    for (int j = 0; j < n; ++j) total += k_s[j * dim + i];
+    dst[(size_t)dim * vdim + i] = total;
+  }
+}
+
+// grid (requests, heads, blocks over dim * vdim + dim + 1 cells: the matrix, the normaliser, the maximum)
+__global__ void __launch_bounds__(256)
+mlstm_chunk_prefix_kernel(float* __restrict__ chunk_sums, float* __restrict__ state, long long state_stride,
+                          const float* __restrict__ gates, const int* __restrict__ request_chunk_start,
+                          const int* __restrict__ chunk_row, const int* __restrict__ chunk_count,
+                          const int* __restrict__ slots, const int* __restrict__ request_active, int heads, int dim,
+                          int vdim, int max_slots, int* err) {
+  pdl_wait();
+  pdl_trigger();
+  const int request = blockIdx.x, head = blockIdx.y;
+  const int e = blockIdx.z * blockDim.x + threadIdx.x;
+  const int matrix = dim * vdim, cells = matrix + dim;
+  if (e > cells) return;
+  const int slot = slots[request];
+  if (slot < 0 || slot >= max_slots) {
+    if (e == 0) atomicOr(err, kErrBadRequest);
+    return;
+  }
+  const int copies = (vdim + kNormaliserColumns - 1) / kNormaliserColumns;
+  const size_t head_floats = (size_t)matrix + (size_t)copies * (dim + 1);
+  float* base = state + (size_t)slot * state_stride + (size_t)head * head_floats;
+  const int first = request_chunk_start[request], last = request_chunk_start[request + 1];
+  const bool active = request_active[request] != 0;
+  if (e == cells) {                 // the running maximum after the request's last token
+    if (active && last > first) {
+      const int t = chunk_row[last - 1] + chunk_count[last - 1] - 1;
+      const float m = gates[((size_t)t * heads + head) * kMemGates + 2];
+      for (int copy = 0; copy < copies; ++copy) base[(size_t)matrix + (size_t)copy * (dim + 1) + dim] = m;
+    }
+    return;
+  }
+  float s = e < matrix ? base[e] : base[(size_t)matrix + (e - matrix)];
+  const size_t stride = (size_t)heads * cells;
+  constexpr int kBatch = 8;         // the sums of eight chunks are asked for together, before the first store
+  for (int chunk = first; chunk < last; chunk += kBatch) {
+    float* u = chunk_sums + ((size_t)chunk * heads + head) * cells + e;
+    float gained[kBatch], power[kBatch];
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      const bool in = chunk + b < last;
+      gained[b] = in ? u[b * stride] : 0.f;
+      power[b] = 1.f;
+      if (in) {
+        const int tf = chunk_row[chunk + b], tl = tf + chunk_count[chunk + b] - 1;
+        const float* gl = gates + ((size_t)tl * heads + head) * kMemGates;
+        power[b] = expf(gl[1] + gates[((size_t)tf * heads + head) * kMemGates + 3] - gl[2]);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      if (chunk + b < last) {
+        u[b * stride] = s;
+        s = fmaf(power[b], s, gained[b]);
+      }
+    }
+  }
+  if (!active) return;
+  if (e < matrix) base[e] = s;
+  else
+    for (int copy = 0; copy < copies; ++copy) base[(size_t)matrix + (size_t)copy * (dim + 1) + (e - matrix)] = s;
+}
+
+// grid (chunks, heads).  chunk_sums holds, after the walk, the state before each chunk.
+__global__ void __launch_bounds__(kMemWarps * 32)
+mlstm_chunk_output_kernel(const float* __restrict__ proj, int proj_stride, int q_off, int k_off, int v_off, float q_scale,
+                          const float* __restrict__ gates, const float* __restrict__ chunk_sums,
+                          float* __restrict__ out, int out_stride, const int* __restrict__ chunk_row,
+                          const int* __restrict__ chunk_count, int heads, int dim, int vdim) {
+  extern __shared__ __align__(16) float smem[];
+  const int kd = dim + 1;                         // k rows are padded by one element: lanes run over keys
+  float* q_s = smem;                              // [kMemChunk][dim]
+  float* v_s = q_s + kMemChunk * dim;             // [kMemChunk][vdim]
+  float* a_s = v_s + kMemChunk * vdim;            // [kMemChunk][kMemChunk]
+  float* k_s = a_s + kMemChunk * kMemChunk;       // [kMemChunk][dim + 1]
+  __shared__ float gi_s[kMemChunk], gb_s[kMemChunk], gm_s[kMemChunk];
+  __shared__ float m_before;
+  pdl_wait();
+  pdl_trigger();
+  const int chunk = blockIdx.x, head = blockIdx.y;
+  const int row0 = chunk_row[chunk], n = chunk_count[chunk];
+  if (threadIdx.x < n) {
+    const float4 g = *reinterpret_cast<const float4*>(gates + ((size_t)(row0 + threadIdx.x) * heads + head) * kMemGates);
+    gi_s[threadIdx.x] = g.x;
+    gb_s[threadIdx.x] = g.y;
+    gm_s[threadIdx.x] = g.z;
+    if (threadIdx.x == 0) m_before = g.w;
+  }
+  stage_rows(q_s, dim, proj, proj_stride, row0, n, q_off + head * dim, dim, [&](int) { return q_scale; });
+  stage_rows(k_s, kd, proj, proj_stride, row0, n, k_off + head * dim, dim, [](int) { return 1.f; });
+  stage_rows(v_s, vdim, proj, proj_stride, row0, n, v_off + head * vdim, vdim, [](int) { return 1.f; });
+  __syncthreads();
+  for (int e = threadIdx.x; e < n * kMemChunk; e += blockDim.x) {
+    const int i = e / kMemChunk, j = e % kMemChunk;
+    float dot = 0.f;
+    if (j <= i) {
+      for (int x = 0; x < dim; ++x) dot = fmaf(q_s[i * dim + x], k_s[j * kd + x], dot);
+      dot *= expf(gb_s[i] - gb_s[j] + gi_s[j] - gm_s[i]);
+    }
+    a_s[e] = dot;
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const size_t cells = (size_t)dim * vdim + dim;
+  const float* before = chunk_sums + ((size_t)chunk * heads + head) * cells;
+  const float* n_before = before + (size_t)dim * vdim;
+  // a warp takes tokens warp, warp + 8, ...; a lane the value columns lane, lane + 32, ...
+  constexpr int kTokens = kMemChunk / kMemWarps;
+  float carried[kTokens], below[kTokens];
+#pragma unroll
+  for (int t = 0; t < kTokens; ++t) {
+    const int i = warp + kMemWarps * t;
+    carried[t] = 0.f;
+    below[t] = 1.f;
+    if (i >= n) continue;
+    carried[t] = expf(gb_s[i] + m_before - gm_s[i]);
+    float nq = 0.f;
+    for (int x = lane; x < dim; x += 32) nq = fmaf(n_before[x], q_s[i * dim + x], nq);
+    nq = warp_sum(nq) * carried[t] + warp_sum(lane <= i ? a_s[i * kMemChunk + lane] : 0.f);
+    below[t] = fmaxf(fabsf(nq), expf(-gm_s[i])) + 1e-6f;
+  }
+  float inter[kTokens][kMemCols] = {}, intra[kTokens][kMemCols] = {};
+  const int dim4 = dim % 4 == 0 ? dim : 0;       // four state rows a step where the q rows allow 16-byte loads
+  for (int x = 0; x < dim4; x += 4) {
+    float sv[4][kMemCols];
+#pragma unroll
+    for (int y = 0; y < 4; ++y)
+#pragma unroll
+      for (int c = 0; c < kMemCols; ++c) sv[y][c] = lane + 32 * c < vdim ? before[(size_t)(x + y) * vdim + lane + 32 * c] : 0.f;
+#pragma unroll
+    for (int t = 0; t < kTokens; ++t) {
+      const int i = warp + kMemWarps * t;
+      const float4 q4 = i < n ? *reinterpret_cast<const float4*>(q_s + i * dim + x) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int c = 0; c < kMemCols; ++c) {
+        inter[t][c] = fmaf(q4.x, sv[0][c], inter[t][c]);
+        inter[t][c] = fmaf(q4.y, sv[1][c], inter[t][c]);
+        inter[t][c] = fmaf(q4.z, sv[2][c], inter[t][c]);
+        inter[t][c] = fmaf(q4.w, sv[3][c], inter[t][c]);
+      }
+    }
+  }
+  for (int x = dim4; x < dim; ++x) {
+    float sv[kMemCols];
+#pragma unroll
+    for (int c = 0; c < kMemCols; ++c) sv[c] = lane + 32 * c < vdim ? before[(size_t)x * vdim + lane + 32 * c] : 0.f;
+#pragma unroll
+    for (int t = 0; t < kTokens; ++t) {
+      const int i = warp + kMemWarps * t;
+      const float qv = i < n ? q_s[i * dim + x] : 0.f;
+#pragma unroll
+      for (int c = 0; c < kMemCols; ++c) inter[t][c] = fmaf(qv, sv[c], inter[t][c]);
+    }
+  }
+  for (int j = 0; j < n; ++j) {
+    float vv[kMemCols];
+#pragma unroll
+    for (int c = 0; c < kMemCols; ++c) vv[c] = lane + 32 * c < vdim ? v_s[j * vdim + lane + 32 * c] : 0.f;
+#pragma unroll
+    for (int t = 0; t < kTokens; ++t) {
+      const int i = warp + kMemWarps * t;
+      const float av = (i < n && j <= i) ? a_s[i * kMemChunk + j] : 0.f;
+#pragma unroll
+      for (int c = 0; c < kMemCols; ++c) intra[t][c] = fmaf(av, vv[c], intra[t][c]);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kTokens; ++t) {
+    const int i = warp + kMemWarps * t;
+    if (i >= n) continue;
+#pragma unroll
+    for (int c = 0; c < kMemCols; ++c)
+      if (lane + 32 * c < vdim)
+        out[(size_t)(row0 + i) * out_stride + head * vdim + lane + 32 * c] = fmaf(carried[t], inter[t][c], intra[t][c]) / below[t];
+  }
+}
+
 // ---------------------------------------------------------------- per-head norm x gain x gate
 // out[t][g*size + i] = gain * o / rms(o over the head) * act(gate); gain index i (shared) or g*size + i.  With
 // `denominators` [tokens][heads], o is first divided by its token's and head's number.
@@ -649,6 +974,51 @@ extern "C" int cie_gated_delta_scan(const float* conv, int conv_stride, int q_of
              request_active, heads, kv_heads, dim, vdim, max_slots, err)
   CIE_SCAN_SHAPES("gated_delta_scan", dim, vdim, CIE_BODY);
 #undef CIE_BODY
+  return 0;
+}
+
+extern "C" int cie_mlstm_chunk_tokens() { return kMemChunk; }
+extern "C" int cie_mlstm_chunk_max_dim() { return kMemDim; }
+
+// Floats of scratch memory the chunked form wants: every token's gates, then every chunk's sums.
+extern "C" long long cie_mlstm_chunk_floats(int tokens, int chunks, int heads, int dim, int vdim) {
+  return (long long)tokens * heads * kMemGates + (long long)chunks * heads * ((long long)dim * vdim + dim);
+}
+
+// The matrix memory over a step with prompt portions, in chunks (work lists from the host: first token row and
+// token count of every chunk, and where every request's chunks start).  `out` gets the mixer's output.
+extern "C" int cie_mlstm_chunked(const float* proj, int proj_stride, int q_off, int k_off, int v_off, int i_off,
+                                 int f_off, const float* i_bias, const float* f_bias, float cap, float q_scale,
+                                 float* scratch, float* out, int out_stride, float* state, long long state_stride,
+                                 const int* query_start, const int* slots, const int* request_active,
+                                 const int* chunk_row, const int* chunk_count, const int* request_chunk_start,
+                                 int tokens, int chunks, int requests, int heads, int dim, int vdim, int max_slots,
+                                 int* err, void* stream) {
+  if (requests <= 0 || tokens <= 0 || chunks <= 0) return 0;
+  if (dim < 1 || dim > kMemDim || vdim < 1 || vdim > kMemDim)
+    CIE_FAIL("mlstm_chunked: key / value sizes %d / %d are outside 1..%d", dim, vdim, kMemDim);
+  if (heads < 1 || heads > 65535) CIE_FAIL("mlstm_chunked: %d heads", heads);
+  if (!(cap > 0.f)) CIE_FAIL("mlstm_chunked: the gate cap must be positive, got %f", cap);
+  cudaStream_t s = (cudaStream_t)stream;
+  float* gates = scratch;
+  float* sums = scratch + (size_t)tokens * heads * kMemGates;
+  const size_t smem2 = (size_t)kMemChunk * (dim + vdim) * sizeof(float);
+  const size_t smem4 = (size_t)kMemChunk * (2 * dim + 1 + vdim + kMemChunk) * sizeof(float);
+  if (smem4 > 48 * 1024 && cudaFuncSetAttribute(mlstm_chunk_output_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)smem4) != cudaSuccess)
+    CIE_FAIL("mlstm_chunked: cannot reserve %zu bytes of shared memory", smem4);
+  const dim3 grid(chunks, heads), block(kMemWarps * 32);
+  CIE_LAUNCH("mlstm_gate_walk", mlstm_gate_walk_kernel, dim3(requests, heads), dim3(32), 0, s, proj, proj_stride, i_off,
+             f_off, i_bias, f_bias, cap, (const float*)state, state_stride, gates, query_start, slots, heads, dim, vdim,
+             max_slots, err);
+  CIE_LAUNCH("mlstm_chunk_sums", mlstm_chunk_sums_kernel, grid, block, smem2, s, proj, proj_stride, k_off, v_off,
+             (const float*)gates, sums, chunk_row, chunk_count, heads, dim, vdim);
+  CIE_LAUNCH("mlstm_chunk_prefix", mlstm_chunk_prefix_kernel, dim3(requests, heads, (dim * vdim + dim + 1 + 255) / 256),
+             dim3(256), 0, s, sums, state, state_stride, (const float*)gates, request_chunk_start, chunk_row, chunk_count,
+             slots, request_active, heads, dim, vdim, max_slots, err);
+  CIE_LAUNCH("mlstm_chunk_output", mlstm_chunk_output_kernel, grid, block, smem4, s, proj, proj_stride, q_off, k_off,
+             v_off, q_scale, (const float*)gates, (const float*)sums, out, out_stride, chunk_row, chunk_count, heads, dim,
+             vdim);
   return 0;
 }
 

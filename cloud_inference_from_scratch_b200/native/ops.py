@@ -391,6 +391,12 @@ class Ops:
             lib.handle.cie_recurrent_stream_floats.restype = ctypes.c_longlong
             self._recurrent_stream_floats = lib.handle.cie_recurrent_stream_floats
             self.stream_max_dim = int(lib.handle.cie_stream_max_dim())
+            self._mlstm_chunked = lib.function(
+                "cie_mlstm_chunked", [v, i, i, i, i, i, i, v, v, f, f, v, v, i, v, ll, v, v, v, v, v, v, i, i, i, i, i, i, i, v, v])
+            lib.handle.cie_mlstm_chunk_floats.restype = ctypes.c_longlong
+            self._mlstm_chunk_floats = lib.handle.cie_mlstm_chunk_floats
+            self.mlstm_chunk_tokens = int(lib.handle.cie_mlstm_chunk_tokens())
+            self.mlstm_chunk_max_dim = int(lib.handle.cie_mlstm_chunk_max_dim())
             self.scan_max_dim = int(lib.handle.cie_scan_max_dim())
             self.conv_max_taps = int(lib.handle.cie_conv_max_taps())
             self.normaliser_columns = int(lib.handle.cie_normaliser_columns())
@@ -408,6 +414,15 @@ class Ops:
         return (tokens >= 8 * ctx.num_requests and dim <= self.stream_max_dim
                 and os.environ.get("CIE_RECURRENT_STREAM", "1") != "0")
 
+    def plan_memory_chunks(self, host: Any) -> dict[str, Any]:
+        """Work lists of the matrix memory's chunked form for a step that holds prompt portions (first token
+        row and token count of every chunk; where every request's chunks start).  A step of single tokens
+        needs none."""
+        if host.num_single == host.num_requests:
+            return {}
+        self._load_recurrent()
+        return self._plan_chunks(host, self.mlstm_chunk_tokens)
+
     def _stream_scratch(self, tokens: int, heads: int, dim: int, vdim: int, memory: bool) -> Any:
         floats = self._recurrent_stream_floats
         return self.scratch(f"recurrent.packed.{heads}x{dim}x{vdim}.{int(memory)}",
@@ -415,7 +430,8 @@ class Ops:
                             reserve=int(floats(max(tokens, self.max_rows), heads, dim, vdim, int(memory))))
 
     def mlstm_scan(self, proj: Any, offsets: tuple[int, int, int, int, int], input_bias: Any, forget_bias: Any,
-                   cap: float, q_scale: float, out: Any, state: Any, ctx: Any, heads: int, dim: int, vdim: int) -> Any:
+                   cap: float, q_scale: float, out: Any, state: Any, ctx: Any, heads: int, dim: int, vdim: int,
+                   plan: dict[str, Any] | None = None) -> Any:
         """Runs the matrix memory (mLSTM) over every request's new tokens from the state in its slot
         (``state``: float32 [slots, heads * (dim * vdim + copies * (dim + 1))]: per head the matrix and then
         the normaliser and the running maximum, once for every ``normaliser_columns`` value columns).  ``proj``
@@ -423,11 +439,30 @@ class Ops:
         [T, heads * vdim].  A step of single tokens runs one kernel and ``out`` is the mixer's output; a step with
         prompt portions first packs what the recurrence reads for all tokens at once and then streams it: ``out``
         then holds the numerators and the float32 [T, heads] tensor that is returned what ``head_norm_gate`` is to
-        divide them by (None otherwise)."""
+        divide them by (None otherwise).  With ``plan`` (``plan_memory_chunks``, on the device) and key and value
+        sizes that the chunk kernels take, prompt portions run in chunks instead: the gates of all tokens, chunk
+        sums in parallel, a short walk over each request's chunks, outputs in parallel; ``out`` is the mixer's
+        output."""
         self._flush()
         self._load_recurrent()
         q_off, k_off, v_off, i_off, f_off = offsets
         tokens = proj.shape[0]
+        if (plan and tokens >= 8 * ctx.num_requests and max(dim, vdim) <= self.mlstm_chunk_max_dim
+                and os.environ.get("CIE_RECURRENT_CHUNKS", "1") != "0"):
+            chunks = plan["chunk_row"].shape[0]
+            floats = int(self._mlstm_chunk_floats(tokens, chunks, heads, dim, vdim))
+            rows = max(tokens, self.max_rows)
+            reserve = int(self._mlstm_chunk_floats(rows, -(-rows // self.mlstm_chunk_tokens) + ctx.num_requests,
+                                                   heads, dim, vdim))
+            scratch = self.scratch(f"recurrent.chunks.{heads}x{dim}x{vdim}", floats, reserve=max(floats, reserve))
+            self.launches += 4
+            self._mlstm_chunked(_ptr(proj), proj.stride(0), q_off, k_off, v_off, i_off, f_off, _ptr(input_bias),
+                                _ptr(forget_bias), float(cap), float(q_scale), _ptr(scratch), _ptr(out), out.stride(0),
+                                _ptr(state), state.stride(0), _ptr(ctx.query_start), _ptr(ctx.slots),
+                                _ptr(ctx.request_active), _ptr(plan["chunk_row"]), _ptr(plan["chunk_count"]),
+                                _ptr(plan["request_chunk_start"]), tokens, chunks, ctx.num_requests, heads, dim, vdim,
+                                state.shape[0], _ptr(self.error_word), self.stream)
+            return None
         if self._streams(tokens, ctx, dim):
             packed = self._stream_scratch(tokens, heads, dim, vdim, True)
             below = self.scratch(f"recurrent.denominators.{heads}", tokens * heads,
@@ -594,7 +629,13 @@ class Ops:
         if host.num_single == host.num_requests:
             return {}
         self._load_lightning()
-        size = self.lightning_chunk_tokens
+        return self._plan_chunks(host, self.lightning_chunk_tokens)
+
+    @staticmethod
+    def _plan_chunks(host: Any, size: int) -> dict[str, Any]:
+        """Every request's new tokens cut into chunks of ``size`` from its first new token."""
+        import numpy as np
+
         rows, counts, starts = [], [], [0]
         for first, length in zip(host.query_start[:-1].tolist(), host.query_lens.tolist()):
             for offset in range(0, length, size):

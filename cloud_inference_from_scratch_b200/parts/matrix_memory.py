@@ -46,6 +46,14 @@ class MatrixMemory(Mixer):
         self.names = {key: key for key in ("q", "k", "v", "g", "i", "i.b", "f", "f.b", "norm", "o")}
         self.names.update(names or {})
 
+    @property
+    def plan_key(self):
+        return ("memory.chunks",)
+
+    def plan(self, host, cache):
+        """Chunk work lists for a step with prompt portions (one list serves every matrix memory)."""
+        return self.runtime.ops.plan_memory_chunks(host)
+
     def state_spec(self) -> StateSpec:
         # per head: the matrix, then the normaliser vector and the running maximum once for every
         # NORMALISER_COLUMNS value columns (the blocks of a scan share no word that one of them writes)
@@ -91,7 +99,8 @@ class MatrixMemory(Mixer):
         mixed = rt.workspace.get("memory.o", tokens, vv, f32)
         below = ops.mlstm_scan(proj, (0, qk, 2 * qk, 2 * qk + 2 * vv, 2 * qk + 2 * vv + heads), self.input_bias,
                                self.forget_bias, self.gate_cap, self.key_dim ** -0.5, mixed, binding.state, ctx,
-                               heads, self.key_dim, self.value_dim)
+                               heads, self.key_dim, self.value_dim,
+                               plan=getattr(ctx, "extras", {}).get(self.plan_key) or None)
         gated = rt.workspace.get("memory.gated", tokens, vv, rt.dtype)
         ops.head_norm_gate(mixed, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.gain, self.eps, gated, heads,
                            denominators=below)

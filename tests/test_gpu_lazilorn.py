@@ -491,13 +491,14 @@ def memory_gates(rows_i, rows_f, bias_i, bias_f, cap):
 
 @pytest.mark.parametrize("heads,dim,vdim,cap", [(3, 20, 36, 9.0), (2, 64, 64, 15.0), (1, 128, 32, 4.0), (2, 5, 130, 1.0),
                                                 (2, 160, 8, 30.0), (1, 64, 300, 9.0), (2, 200, 136, 9.0)])
-@pytest.mark.parametrize("streams", ["1", "0"])
+@pytest.mark.parametrize("streams", ["chunks", "1", "0"])
 def test_matrix_memory_carries_matrix_normaliser_and_maximum_between_steps(heads, dim, vdim, cap, streams, monkeypatch):
-    """Prompt portions as prepare + stream (keys up to 128) or on the token-by-token kernel.  Three steps of unequal requests (portions of 1 to 100 tokens, so every kernel for prompts and for
+    """Prompt portions in chunks (keys and values up to 128), as prepare + stream (keys up to 128) or on the
+    token-by-token kernel.  Three steps of unequal requests (portions of 1 to 100 tokens, so every kernel for prompts and for
     single tokens runs) from states that are not zero, one request inactive in the second step (its state
     must stay); gates with large biases either way, so that the running maximum moves and the floor
     exp(-m) of the denominator is what counts for some tokens and |n . q| for others."""
-    monkeypatch.setenv("CIE_RECURRENT_STREAM", streams)
+    monkeypatch.setenv("CIE_RECURRENT_STREAM", "0" if streams == "0" else "1")
     rt = runtime("float32")
     qk, vv = heads * dim, heads * vdim
     width = 2 * qk + 2 * vv + 2 * heads
@@ -520,10 +521,15 @@ def test_matrix_memory_carries_matrix_normaliser_and_maximum_between_steps(heads
         proj[:, offsets[3]:] *= 4.0
         ctx, starts = scan_ctx(lengths, slots, active)
         out = torch.empty(tokens, vv, dtype=torch.float32).cuda()
+        plan = None
+        if streams == "chunks":
+            plan = {name: torch.from_numpy(a).cuda() for name, a in rt.ops.plan_memory_chunks(ctx.host).items()}
         below = rt.ops.mlstm_scan(proj.cuda(), offsets, bias_i.cuda(), bias_f.cuda(), cap, dim ** -0.5, out, state,
-                                  ctx, heads, dim, vdim)
+                                  ctx, heads, dim, vdim, plan=plan)
         rt.ops.check_errors()
-        assert (below is not None) == (streams == "1" and dim <= 128 and tokens >= 8 * len(lengths))
+        wide = tokens >= 8 * len(lengths)
+        chunked = streams == "chunks" and wide and bool(plan) and max(dim, vdim) <= 128
+        assert (below is not None) == (streams != "0" and not chunked and dim <= 128 and wide)
         if below is not None:          # the stream leaves numerators and what the head norm divides them by
             out = (out.view(tokens, heads, vdim) / below.unsqueeze(2)).view(tokens, vv)
         for r in range(len(lengths)):
