@@ -398,6 +398,7 @@ gated_delta_prepare_kernel(const float* __restrict__ conv, int conv_stride, int 
     float g = 0.f;
     if (tid == 0) g = expf(-expf(a_log[head]) * softplus_f(proj[(size_t)t * proj_stride + a_off + head] + dt_bias[head]));
     if (tid == 1) g = sigmoid_f(proj[(size_t)t * proj_stride + b_off + head]);
+    if (tid == 2) g = -expf(a_log[head]) * softplus_f(proj[(size_t)t * proj_stride + a_off + head] + dt_bias[head]);   // log of the decay
     dst[2 * pad + tid] = g;
   }
   for (int i = tid; i < vpad; i += blockDim.x) dst[2 * pad + kStreamGates + i] = i < vdim ? row[v_off + head * vdim + i] : 0.f;
@@ -574,7 +575,7 @@ recurrent_stream_kernel(const float* __restrict__ packed, float* __restrict__ ou
 // prompt portion can be cut into chunks of kMemChunk tokens that many CTAs work on at once.  With b_t the log
 // forget gates summed from the chunk's first token to t, m_t the running maximum (the recurrence above, taken
 // token by token so that it is the same number in every form) and m_c the maximum before the chunk:
-//   1. per (request, head), one warp:   the gates of every token: i_t, b_t, m_t, m_(t-1)
+//   1. per token and head the two log gates; then per (request, head), a lane each: b_t, m_t, m_(t-1)
 //   2. per (chunk, head):               U = sum_s exp(b_last - b_s + i_s - m_last) k_s v_s^T, and the same with k_s alone
 //   3. per (request, head):             walks its chunks, S <- exp(b_last + m_c - m_last) S + U, leaving in U's place
 //                                       the state BEFORE the chunk; the last S, n and m go back to the slot
@@ -591,48 +592,58 @@ constexpr int kMemRows = kMemDim / kMemWarps;    // state rows of a warp
 constexpr int kMemCols = kMemDim / 32;           // value columns of a lane
 constexpr int kMemGates = 4;                     // floats per token and head: i_t, b_t, m_t, m_(t-1)
 
-// grid (requests, heads); one warp
+// grid over tokens x heads: the two log gates of every token and head, left in the first two floats of its gates
+__global__ void __launch_bounds__(256)
+mlstm_gates_kernel(const float* __restrict__ proj, int proj_stride, int i_off, int f_off, const float* __restrict__ i_bias,
+                   const float* __restrict__ f_bias, float cap, float* __restrict__ gates, int tokens, int heads) {
+  pdl_wait();
+  pdl_trigger();
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= tokens * heads) return;
+  const int t = e / heads, head = e % heads;
+  const float* row = proj + (size_t)t * proj_stride;
+  const float gi = cap * tanhf((row[i_off + head] + i_bias[head]) / cap);
+  const float gf = log_sigmoid_f(cap * tanhf((row[f_off + head] + f_bias[head]) / cap));
+  *reinterpret_cast<float2*>(gates + (size_t)e * kMemGates) = make_float2(gi, gf);
+}
+
+// grid (requests, blocks of 32 heads); a lane a head.  The chain of a head is one addition and one maximum a
+// token; the gates of eight tokens are asked for together, ahead of the chain.
 __global__ void __launch_bounds__(32)
-mlstm_gate_walk_kernel(const float* __restrict__ proj, int proj_stride, int i_off, int f_off,
-                       const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
-                       const float* __restrict__ state, long long state_stride, float* __restrict__ gates,
+mlstm_gate_walk_kernel(const float* __restrict__ state, long long state_stride, float* __restrict__ gates,
                        const int* __restrict__ query_start, const int* __restrict__ slots, int heads, int dim, int vdim,
                        int max_slots, int* err) {
   pdl_wait();
   pdl_trigger();
-  const int request = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  const int request = blockIdx.x, head = blockIdx.y * 32 + threadIdx.x;
   const int slot = slots[request];
   if (slot < 0 || slot >= max_slots) {
-    if (lane == 0) atomicOr(err, kErrBadRequest);
+    if (threadIdx.x == 0) atomicOr(err, kErrBadRequest);
     return;
   }
+  if (head >= heads) return;
   const int begin = query_start[request], end = query_start[request + 1];
   const int copies = (vdim + kNormaliserColumns - 1) / kNormaliserColumns;
   const size_t head_floats = (size_t)dim * vdim + (size_t)copies * (dim + 1);
   float m = state[(size_t)slot * state_stride + (size_t)head * head_floats + (size_t)dim * vdim + dim];
-  const float bi = i_bias[head], bf = f_bias[head];
-  for (int t0 = begin; t0 < end; t0 += kMemChunk) {
-    const int t = t0 + lane, n = min(kMemChunk, end - t0);
-    float gi = 0.f, gf = 0.f;
-    if (t < end) {
-      const float* row = proj + (size_t)t * proj_stride;
-      gi = cap * tanhf((row[i_off + head] + bi) / cap);
-      gf = log_sigmoid_f(cap * tanhf((row[f_off + head] + bf) / cap));
-    }
-    float b = 0.f, my_b = 0.f, my_m = 0.f, my_before = 0.f;
-    for (int j = 0; j < n; ++j) {
-      const float fj = __shfl_sync(0xffffffffu, gf, j), ij = __shfl_sync(0xffffffffu, gi, j);
-      b += fj;
-      const float m_new = fmaxf(fj + m, ij);
-      if (lane == j) {
-        my_b = b;
-        my_before = m;
-        my_m = m_new;
-      }
+  float b = 0.f;
+  constexpr int kAhead = 8;
+  static_assert(kMemChunk % kAhead == 0, "a chunk starts at a multiple of the tokens taken together");
+  for (int t0 = begin; t0 < end; t0 += kAhead) {
+    float2 g[kAhead];
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u)
+      g[u] = t0 + u < end ? *reinterpret_cast<const float2*>(gates + ((size_t)(t0 + u) * heads + head) * kMemGates)
+                          : make_float2(0.f, 0.f);
+    if ((t0 - begin) % kMemChunk == 0) b = 0.f;
+#pragma unroll
+    for (int u = 0; u < kAhead; ++u) {
+      if (t0 + u >= end) break;
+      b += g[u].y;
+      const float m_new = fmaxf(g[u].y + m, g[u].x);
+      *reinterpret_cast<float4*>(gates + ((size_t)(t0 + u) * heads + head) * kMemGates) = make_float4(g[u].x, b, m_new, m);
       m = m_new;
     }
-    if (t < end)
-      *reinterpret_cast<float4*>(gates + ((size_t)t * heads + head) * kMemGates) = make_float4(gi, my_b, my_m, my_before);
   }
 }
 
@@ -781,11 +792,21 @@ mlstm_chunk_prefix_kernel(float* __restrict__ chunk_sums, float* __restrict__ st
 }
 
 // grid (chunks, heads).  chunk_sums holds, after the walk, the state before each chunk.
+// kMemory: the matrix memory (a denominator from the normaliser); else the gated delta rule in chunks (below), whose
+// rows come with i_t = m_t = 0, b_t = the log decays summed from the chunk's first token, and v = the chunk's writes.
+// q, k, v: where a head's rows are (see RowsOf).
+struct RowsOf {
+  const float* base;      // row t of head h starts at base + h * head_base + t * stride + col0 + h * head_col
+  long long head_base;
+  int stride, col0, head_col;
+};
+
+template <bool kMemory>
 __global__ void __launch_bounds__(kMemWarps * 32)
-mlstm_chunk_output_kernel(const float* __restrict__ proj, int proj_stride, int q_off, int k_off, int v_off, float q_scale,
-                          const float* __restrict__ gates, const float* __restrict__ chunk_sums,
-                          float* __restrict__ out, int out_stride, const int* __restrict__ chunk_row,
-                          const int* __restrict__ chunk_count, int heads, int dim, int vdim) {
+chunk_output_kernel(RowsOf q_rows, RowsOf k_rows, RowsOf v_rows, float q_scale,
+                    const float* __restrict__ gates, const float* __restrict__ chunk_sums,
+                    float* __restrict__ out, int out_stride, const int* __restrict__ chunk_row,
+                    const int* __restrict__ chunk_count, int heads, int dim, int vdim) {
   extern __shared__ __align__(16) float smem[];
   const int kd = dim + 1;                         // k rows are padded by one element: lanes run over keys
   float* q_s = smem;                              // [kMemChunk][dim]
@@ -805,9 +826,12 @@ mlstm_chunk_output_kernel(const float* __restrict__ proj, int proj_stride, int q
     gm_s[threadIdx.x] = g.z;
     if (threadIdx.x == 0) m_before = g.w;
   }
-  stage_rows(q_s, dim, proj, proj_stride, row0, n, q_off + head * dim, dim, [&](int) { return q_scale; });
-  stage_rows(k_s, kd, proj, proj_stride, row0, n, k_off + head * dim, dim, [](int) { return 1.f; });
-  stage_rows(v_s, vdim, proj, proj_stride, row0, n, v_off + head * vdim, vdim, [](int) { return 1.f; });
+  stage_rows(q_s, dim, q_rows.base + head * q_rows.head_base, q_rows.stride, row0, n, q_rows.col0 + head * q_rows.head_col,
+             dim, [&](int) { return q_scale; });
+  stage_rows(k_s, kd, k_rows.base + head * k_rows.head_base, k_rows.stride, row0, n, k_rows.col0 + head * k_rows.head_col,
+             dim, [](int) { return 1.f; });
+  stage_rows(v_s, vdim, v_rows.base + head * v_rows.head_base, v_rows.stride, row0, n, v_rows.col0 + head * v_rows.head_col,
+             vdim, [](int) { return 1.f; });
   __syncthreads();
   for (int e = threadIdx.x; e < n * kMemChunk; e += blockDim.x) {
     const int i = e / kMemChunk, j = e % kMemChunk;
@@ -820,7 +844,7 @@ mlstm_chunk_output_kernel(const float* __restrict__ proj, int proj_stride, int q
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const size_t cells = (size_t)dim * vdim + dim;
+  const size_t cells = (size_t)dim * vdim + (kMemory ? dim : 0);
   const float* before = chunk_sums + ((size_t)chunk * heads + head) * cells;
   const float* n_before = before + (size_t)dim * vdim;
   // a warp takes tokens warp, warp + 8, ...; a lane the value columns lane, lane + 32, ...
@@ -833,6 +857,7 @@ mlstm_chunk_output_kernel(const float* __restrict__ proj, int proj_stride, int q
     below[t] = 1.f;
     if (i >= n) continue;
     carried[t] = expf(gb_s[i] + m_before - gm_s[i]);
+    if (!kMemory) continue;
     float nq = 0.f;
     for (int x = lane; x < dim; x += 32) nq = fmaf(n_before[x], q_s[i * dim + x], nq);
     nq = warp_sum(nq) * carried[t] + warp_sum(lane <= i ? a_s[i * kMemChunk + lane] : 0.f);
@@ -892,6 +917,203 @@ mlstm_chunk_output_kernel(const float* __restrict__ proj, int proj_stride, int q
       if (lane + 32 * c < vdim)
         out[(size_t)(row0 + i) * out_stride + head * vdim + lane + 32 * c] = fmaf(carried[t], inter[t][c], intra[t][c]) / below[t];
   }
+}
+
+// ---------------------------------------------------------------- gated delta rule over prompt portions, in chunks
+// Within a chunk of tokens 1..C that starts from the state S_0, with c_t the decays multiplied from the chunk's first
+// token to t, the rule's writes u_t obey  u_t = b_t (v_t - c_t S_0^T k_t - sum_(s<t) (c_t / c_s) (k_s . k_t) u_s),  a
+// triangular system:  (I + A) U = diag(b) (V - diag(c) K S_0),  A_ts = b_t (c_t / c_s) (k_t . k_s) for s < t.  With
+// T = (I + A)^-1:  U = T diag(b) V - (T diag(b c) K) S_0 = U' - W S_0.  So:
+//   1. prepare (above): unit k and q, decay, write strength and log decay of every token
+//   2. per (chunk, head):      A, T by forward substitution (a lane a column of T), U' and W
+//   3. per (request, head, 32 value columns): walks the chunks with its columns of S in registers:
+//                              U = U' - W S_0,  S <- c_C S_0 + sum_s (c_C / c_s) k_s u_s^T; leaves S_0 of every chunk
+//   4. per (chunk, head):      o_t = c_t S_0^T q_t + sum_(s<=t) (c_t / c_s) (q_t . k_s) u_s   (the matrix memory's output
+//                              kernel with i = m = 0 and no denominator)
+// Ratios of decays are exponentials of differences of summed logarithms, never quotients.  Float32 on the CUDA cores.
+// Keys up to kMemDim, values a multiple of 4.
+constexpr int kWalkColumns = 32;
+
+// grid (chunks, heads).  packed: the prepared rows [k: P][q: P][gates][v: VP] per head and token.
+__global__ void __launch_bounds__(256)
+delta_chunk_solve_kernel(const float* __restrict__ packed, int tokens, int row_floats, int P,
+                         float* __restrict__ gates, float* __restrict__ w_out, float* __restrict__ u_out,
+                         const int* __restrict__ chunk_row, const int* __restrict__ chunk_count, int heads, int vdim) {
+  constexpr int C = kMemChunk;
+  extern __shared__ __align__(16) float smem[];
+  const int kd = P + 1;
+  float* v_s = smem;                       // [C][vdim]
+  float* k_s = v_s + C * vdim;             // [C][P + 1]
+  float* a_s = k_s + C * kd;               // [C][C + 1]
+  float* t_s = a_s + C * (C + 1);          // [C][C + 1]
+  __shared__ float beta_s[C], lg_s[C], bc_s[C];
+  pdl_wait();
+  pdl_trigger();
+  const int chunk = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+  const int row0 = chunk_row[chunk], n = chunk_count[chunk];
+  const float* rows = packed + (size_t)head * tokens * row_floats;
+  if (tid < n) {
+    float lg = 0.f;
+    for (int r = 0; r <= tid; ++r) lg += rows[(size_t)(row0 + r) * row_floats + 2 * P + 2];
+    const float beta = rows[(size_t)(row0 + tid) * row_floats + 2 * P + 1];
+    lg_s[tid] = lg;
+    beta_s[tid] = beta;
+    bc_s[tid] = beta * expf(lg);
+    *reinterpret_cast<float4*>(gates + ((size_t)(row0 + tid) * heads + head) * kMemGates) = make_float4(0.f, lg, 0.f, 0.f);
+  }
+  stage_rows(k_s, kd, rows, row_floats, row0, n, 0, P, [](int) { return 1.f; });
+  stage_rows(v_s, vdim, rows, row_floats, row0, n, 2 * P + kStreamGates, vdim, [](int) { return 1.f; });
+  __syncthreads();
+  for (int e = tid; e < C * C; e += blockDim.x) {
+    const int t = e / C, j = e % C;
+    float a = 0.f;
+    if (j < t && t < n) {
+      for (int x = 0; x < P; ++x) a = fmaf(k_s[t * kd + x], k_s[j * kd + x], a);
+      a *= beta_s[t] * expf(lg_s[t] - lg_s[j]);
+    }
+    a_s[t * (C + 1) + j] = a;
+  }
+  __syncthreads();
+  if (tid < C) {            // column tid of T = (I + A)^-1: T_tj = [t = j] - sum_(s<t) A_ts T_sj
+    float col[C];
+#pragma unroll
+    for (int t = 0; t < C; ++t) {
+      float x = t == tid ? 1.f : 0.f;
+#pragma unroll
+      for (int j = 0; j < t; ++j) x = fmaf(-a_s[t * (C + 1) + j], col[j], x);
+      col[t] = x;
+      t_s[t * (C + 1) + tid] = x;
+    }
+  }
+  __syncthreads();
+  const int wide = vdim + P;
+  for (int e = tid; e < n * wide; e += blockDim.x) {
+    const int t = e / wide, c = e % wide;
+    float acc = 0.f;
+    if (c < vdim) {
+      for (int j = 0; j <= t; ++j) acc = fmaf(t_s[t * (C + 1) + j] * beta_s[j], v_s[j * vdim + c], acc);
+      u_out[((size_t)(row0 + t) * heads + head) * vdim + c] = acc;
+    } else {
+      const int x = c - vdim;
+      for (int j = 0; j <= t; ++j) acc = fmaf(t_s[t * (C + 1) + j] * bc_s[j], k_s[j * kd + x], acc);
+      w_out[((size_t)(row0 + t) * heads + head) * P + x] = acc;
+    }
+  }
+}
+
+// grid (requests, heads, blocks of kWalkColumns value columns); 256 threads: warp w keeps state rows 16 w .. 16 w + 15
+// of the block's columns in registers, a lane a column.  What a chunk brings (W, k, U', the summed log decays) comes
+// through two cp.async stages, a chunk ahead.
+__global__ void __launch_bounds__(256)
+delta_chunk_walk_kernel(const float* __restrict__ packed, int tokens, int row_floats, int P,
+                        const float* __restrict__ gates, const float* __restrict__ w_in, float* __restrict__ u_io,
+                        float* __restrict__ before, float* __restrict__ state, long long state_stride,
+                        const int* __restrict__ request_chunk_start, const int* __restrict__ chunk_row,
+                        const int* __restrict__ chunk_count, const int* __restrict__ slots,
+                        const int* __restrict__ request_active, int heads, int dim, int vdim, int max_slots, int* err) {
+  constexpr int C = kMemChunk, kRows = kMemRows, kCols = kWalkColumns;
+  extern __shared__ __align__(16) float smem[];
+  const int stage_floats = 2 * C * P + C * kCols + C * kMemGates;
+  float* part_s = smem + 2 * stage_floats;        // [warps][C][kCols]
+  float* u_s = part_s + kMemWarps * C * kCols;    // [C][kCols]
+  pdl_wait();
+  pdl_trigger();
+  const int request = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * kCols, tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31, column = col0 + lane, r0 = warp * kRows;
+  const int slot = slots[request];
+  if (slot < 0 || slot >= max_slots) {
+    if (tid == 0) atomicOr(err, kErrBadRequest);
+    return;
+  }
+  const bool live = column < vdim;
+  const int warps = P / kRows;                     // warps that hold rows
+  float* s_base = state + (size_t)slot * state_stride + (size_t)head * dim * vdim;
+  float s[kRows];
+#pragma unroll
+  for (int r = 0; r < kRows; ++r) s[r] = (live && r0 + r < dim) ? s_base[(size_t)(r0 + r) * vdim + column] : 0.f;
+  const int first = request_chunk_start[request], last = request_chunk_start[request + 1];
+  const float* rows = packed + (size_t)head * tokens * row_floats;
+  const int columns = min(kCols, vdim - col0);     // a multiple of 4, as vdim is
+  auto issue = [&](int chunk) {
+    if (chunk < last) {
+      float* dst = smem + (size_t)((chunk - first) & 1) * stage_floats;
+      const int row0 = chunk_row[chunk], n = chunk_count[chunk];
+      const int pw = P / 4, pu = columns / 4;
+      for (int c = tid; c < n * pw; c += blockDim.x) {
+        const int t = c / pw, piece = c % pw;
+        stream_cp_async16(dst + t * P + 4 * piece, w_in + ((size_t)(row0 + t) * heads + head) * P + 4 * piece);
+        stream_cp_async16(dst + C * P + t * P + 4 * piece, rows + (size_t)(row0 + t) * row_floats + 4 * piece);
+      }
+      for (int c = tid; c < n * pu; c += blockDim.x) {
+        const int t = c / pu, piece = c % pu;
+        stream_cp_async16(dst + 2 * C * P + t * kCols + 4 * piece,
+                          u_io + ((size_t)(row0 + t) * heads + head) * vdim + col0 + 4 * piece);
+      }
+      for (int t = tid; t < n; t += blockDim.x)
+        stream_cp_async16(dst + 2 * C * P + C * kCols + t * kMemGates, gates + ((size_t)(row0 + t) * heads + head) * kMemGates);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  issue(first);
+  for (int chunk = first; chunk < last; ++chunk) {
+    const float* w_s = smem + (size_t)((chunk - first) & 1) * stage_floats;
+    const float* k_s = w_s + C * P;
+    const float* ut_s = k_s + C * P;
+    const float* g_s = ut_s + C * kCols;
+    const int row0 = chunk_row[chunk], n = chunk_count[chunk];
+    issue(chunk + 1);
+    asm volatile("cp.async.wait_group 1;\n" ::);
+    __syncthreads();
+    if (warp < warps) {
+      float* dst = before + ((size_t)chunk * heads + head) * dim * vdim;
+#pragma unroll
+      for (int r = 0; r < kRows; ++r)
+        if (live && r0 + r < dim) dst[(size_t)(r0 + r) * vdim + column] = s[r];
+      for (int t = 0; t < n; ++t) {
+        float acc = 0.f;
+#pragma unroll
+        for (int r = 0; r < kRows; r += 4) {
+          const float4 w4 = *reinterpret_cast<const float4*>(w_s + t * P + r0 + r);
+          acc = fmaf(w4.x, s[r], acc);
+          acc = fmaf(w4.y, s[r + 1], acc);
+          acc = fmaf(w4.z, s[r + 2], acc);
+          acc = fmaf(w4.w, s[r + 3], acc);
+        }
+        part_s[(warp * C + t) * kCols + lane] = acc;
+      }
+    }
+    __syncthreads();
+    for (int t = warp; t < n; t += kMemWarps) {
+      float u = ut_s[t * kCols + lane];
+      for (int w = 0; w < warps; ++w) u -= part_s[(w * C + t) * kCols + lane];
+      u_s[t * kCols + lane] = u;
+      if (live) u_io[((size_t)(row0 + t) * heads + head) * vdim + column] = u;
+    }
+    __syncthreads();
+    if (warp < warps) {
+      const float lg_last = g_s[(n - 1) * kMemGates + 1];
+      const float keep = expf(lg_last);
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) s[r] *= keep;
+      for (int t = 0; t < n; ++t) {
+        const float u = u_s[t * kCols + lane] * expf(lg_last - g_s[t * kMemGates + 1]);
+#pragma unroll
+        for (int r = 0; r < kRows; r += 4) {
+          const float4 k4 = *reinterpret_cast<const float4*>(k_s + t * P + r0 + r);
+          s[r] = fmaf(k4.x, u, s[r]);
+          s[r + 1] = fmaf(k4.y, u, s[r + 1]);
+          s[r + 2] = fmaf(k4.z, u, s[r + 2]);
+          s[r + 3] = fmaf(k4.w, u, s[r + 3]);
+        }
+      }
+    }
+    __syncthreads();        // everybody is done with this chunk's stage and with u_s before they are filled again
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::);
+  if (!request_active[request] || !live) return;
+#pragma unroll
+  for (int r = 0; r < kRows; ++r)
+    if (r0 + r < dim) s_base[(size_t)(r0 + r) * vdim + column] = s[r];
 }
 
 // ---------------------------------------------------------------- per-head norm x gain x gate
@@ -1004,21 +1226,77 @@ extern "C" int cie_mlstm_chunked(const float* proj, int proj_stride, int q_off, 
   float* sums = scratch + (size_t)tokens * heads * kMemGates;
   const size_t smem2 = (size_t)kMemChunk * (dim + vdim) * sizeof(float);
   const size_t smem4 = (size_t)kMemChunk * (2 * dim + 1 + vdim + kMemChunk) * sizeof(float);
-  if (smem4 > 48 * 1024 && cudaFuncSetAttribute(mlstm_chunk_output_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (smem4 > 48 * 1024 && cudaFuncSetAttribute(chunk_output_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                 (int)smem4) != cudaSuccess)
     CIE_FAIL("mlstm_chunked: cannot reserve %zu bytes of shared memory", smem4);
   const dim3 grid(chunks, heads), block(kMemWarps * 32);
-  CIE_LAUNCH("mlstm_gate_walk", mlstm_gate_walk_kernel, dim3(requests, heads), dim3(32), 0, s, proj, proj_stride, i_off,
-             f_off, i_bias, f_bias, cap, (const float*)state, state_stride, gates, query_start, slots, heads, dim, vdim,
-             max_slots, err);
+  CIE_LAUNCH("mlstm_gates", mlstm_gates_kernel, dim3((tokens * heads + 255) / 256), dim3(256), 0, s, proj, proj_stride,
+             i_off, f_off, i_bias, f_bias, cap, gates, tokens, heads);
+  CIE_LAUNCH("mlstm_gate_walk", mlstm_gate_walk_kernel, dim3(requests, (heads + 31) / 32), dim3(32), 0, s,
+             (const float*)state, state_stride, gates, query_start, slots, heads, dim, vdim, max_slots, err);
   CIE_LAUNCH("mlstm_chunk_sums", mlstm_chunk_sums_kernel, grid, block, smem2, s, proj, proj_stride, k_off, v_off,
              (const float*)gates, sums, chunk_row, chunk_count, heads, dim, vdim);
   CIE_LAUNCH("mlstm_chunk_prefix", mlstm_chunk_prefix_kernel, dim3(requests, heads, (dim * vdim + dim + 1 + 255) / 256),
              dim3(256), 0, s, sums, state, state_stride, (const float*)gates, request_chunk_start, chunk_row, chunk_count,
              slots, request_active, heads, dim, vdim, max_slots, err);
-  CIE_LAUNCH("mlstm_chunk_output", mlstm_chunk_output_kernel, grid, block, smem4, s, proj, proj_stride, q_off, k_off,
-             v_off, q_scale, (const float*)gates, (const float*)sums, out, out_stride, chunk_row, chunk_count, heads, dim,
-             vdim);
+  const RowsOf q_rows{proj, 0, proj_stride, q_off, dim}, k_rows{proj, 0, proj_stride, k_off, dim}, v_rows{proj, 0, proj_stride, v_off, vdim};
+  CIE_LAUNCH("mlstm_chunk_output", chunk_output_kernel<true>, grid, block, smem4, s, q_rows, k_rows, v_rows, q_scale,
+             (const float*)gates, (const float*)sums, out, out_stride, chunk_row, chunk_count, heads, dim, vdim);
+  return 0;
+}
+
+// Floats of scratch memory the gated delta rule in chunks wants: the prepared rows, every token's summed log decays,
+// W and U per token, and the state before every chunk.
+extern "C" long long cie_gated_delta_chunk_floats(int tokens, int chunks, int heads, int dim, int vdim) {
+  const long long row = 2 * stream_pad(dim) + kStreamGates + stream_value_pad(dim, vdim, false);
+  return (long long)tokens * heads * (row + kMemGates + stream_pad(dim) + vdim) + (long long)chunks * heads * dim * vdim;
+}
+
+// The gated delta rule over a step with prompt portions, in chunks of cie_mlstm_chunk_tokens() tokens (work lists as
+// for the matrix memory).  Keys up to cie_mlstm_chunk_max_dim(), values up to the same and a multiple of 4.
+extern "C" int cie_gated_delta_chunked(const float* conv, int conv_stride, int q_off, int k_off, int v_off,
+                                       const float* proj, int proj_stride, int b_off, int a_off, const float* a_log,
+                                       const float* dt_bias, float q_scale, float* scratch, float* out, int out_stride,
+                                       float* state, long long state_stride, const int* slots, const int* request_active,
+                                       const int* chunk_row, const int* chunk_count, const int* request_chunk_start,
+                                       int tokens, int chunks, int requests, int heads, int kv_heads, int dim, int vdim,
+                                       int max_slots, int* err, void* stream) {
+  if (requests <= 0 || tokens <= 0 || chunks <= 0) return 0;
+  if (dim < 1 || dim > kMemDim || vdim < 4 || vdim > kMemDim || vdim % 4)
+    CIE_FAIL("gated_delta_chunked: key / value sizes %d / %d (keys up to %d, values a multiple of 4 up to %d)", dim, vdim,
+             kMemDim, kMemDim);
+  if (heads < 1 || heads > 65535 || kv_heads < 1 || heads % kv_heads)
+    CIE_FAIL("gated_delta_chunked: %d heads do not divide over %d q/k heads", heads, kv_heads);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int P = stream_pad(dim), row_floats = 2 * P + kStreamGates + stream_value_pad(dim, vdim, false);
+  float* packed = scratch;
+  float* gates = packed + (size_t)tokens * heads * row_floats;
+  float* w = gates + (size_t)tokens * heads * kMemGates;
+  float* u = w + (size_t)tokens * heads * P;
+  float* before = u + (size_t)tokens * heads * vdim;
+  const size_t smem2 = (size_t)(kMemChunk * (vdim + P + 1) + 2 * kMemChunk * (kMemChunk + 1)) * sizeof(float);
+  const size_t smem3 = (size_t)(2 * (2 * kMemChunk * P + kMemChunk * kWalkColumns + kMemChunk * kMemGates) +
+                                (kMemWarps + 1) * kMemChunk * kWalkColumns) * sizeof(float);
+  const size_t smem4 = (size_t)kMemChunk * (2 * dim + 1 + vdim + kMemChunk) * sizeof(float);
+  if (cudaFuncSetAttribute(delta_chunk_solve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2) != cudaSuccess ||
+      cudaFuncSetAttribute(delta_chunk_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3) != cudaSuccess ||
+      cudaFuncSetAttribute(chunk_output_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4) != cudaSuccess)
+    CIE_FAIL("gated_delta_chunked: cannot reserve %zu / %zu / %zu bytes of shared memory", smem2, smem3, smem4);
+  CIE_LAUNCH("gated_delta_prepare", gated_delta_prepare_kernel, dim3(tokens, heads), dim3(128), 0, s, conv, conv_stride,
+             q_off, k_off, v_off, proj, proj_stride, b_off, a_off, a_log, dt_bias, q_scale, packed, tokens, heads, kv_heads,
+             dim, vdim);
+  const dim3 grid(chunks, heads);
+  CIE_LAUNCH("delta_chunk_solve", delta_chunk_solve_kernel, grid, dim3(256), smem2, s, (const float*)packed, tokens,
+             row_floats, P, gates, w, u, chunk_row, chunk_count, heads, vdim);
+  CIE_LAUNCH("delta_chunk_walk", delta_chunk_walk_kernel, dim3(requests, heads, (vdim + kWalkColumns - 1) / kWalkColumns),
+             dim3(256), smem3, s, (const float*)packed, tokens, row_floats, P, (const float*)gates, (const float*)w, u,
+             before, state, state_stride, request_chunk_start, chunk_row, chunk_count, slots, request_active, heads, dim,
+             vdim, max_slots, err);
+  const RowsOf q_rows{packed, (long long)tokens * row_floats, row_floats, P, 0};
+  const RowsOf k_rows{packed, (long long)tokens * row_floats, row_floats, 0, 0};
+  const RowsOf v_rows{u, 0, heads * vdim, 0, vdim};
+  CIE_LAUNCH("delta_chunk_output", chunk_output_kernel<false>, grid, dim3(kMemWarps * 32), smem4, s, q_rows, k_rows, v_rows,
+             1.f, (const float*)gates, (const float*)before, out, out_stride, chunk_row, chunk_count, heads, dim, vdim);
   return 0;
 }
 

@@ -393,6 +393,11 @@ class Ops:
             self.stream_max_dim = int(lib.handle.cie_stream_max_dim())
             self._mlstm_chunked = lib.function(
                 "cie_mlstm_chunked", [v, i, i, i, i, i, i, v, v, f, f, v, v, i, v, ll, v, v, v, v, v, v, i, i, i, i, i, i, i, v, v])
+            self._gated_delta_chunked = lib.function(
+                "cie_gated_delta_chunked",
+                [v, i, i, i, i, v, i, i, i, v, v, f, v, v, i, v, ll, v, v, v, v, v, i, i, i, i, i, i, i, i, v, v])
+            lib.handle.cie_gated_delta_chunk_floats.restype = ctypes.c_longlong
+            self._gated_delta_chunk_floats = lib.handle.cie_gated_delta_chunk_floats
             lib.handle.cie_mlstm_chunk_floats.restype = ctypes.c_longlong
             self._mlstm_chunk_floats = lib.handle.cie_mlstm_chunk_floats
             self.mlstm_chunk_tokens = int(lib.handle.cie_mlstm_chunk_tokens())
@@ -455,7 +460,7 @@ class Ops:
             reserve = int(self._mlstm_chunk_floats(rows, -(-rows // self.mlstm_chunk_tokens) + ctx.num_requests,
                                                    heads, dim, vdim))
             scratch = self.scratch(f"recurrent.chunks.{heads}x{dim}x{vdim}", floats, reserve=max(floats, reserve))
-            self.launches += 4
+            self.launches += 5
             self._mlstm_chunked(_ptr(proj), proj.stride(0), q_off, k_off, v_off, i_off, f_off, _ptr(input_bias),
                                 _ptr(forget_bias), float(cap), float(q_scale), _ptr(scratch), _ptr(out), out.stride(0),
                                 _ptr(state), state.stride(0), _ptr(ctx.query_start), _ptr(ctx.slots),
@@ -496,17 +501,36 @@ class Ops:
 
     def gated_delta_scan(self, conv: Any, offsets: tuple[int, int, int], proj: Any, gate_offsets: tuple[int, int],
                          a_log: Any, dt_bias: Any, q_scale: float, out: Any, state: Any, ctx: Any, heads: int,
-                         kv_heads: int, dim: int, vdim: int) -> None:
+                         kv_heads: int, dim: int, vdim: int, plan: dict[str, Any] | None = None) -> None:
         """Runs the gated delta rule over every request's new tokens from the state in its slot (``state``:
         float32 [slots, >= heads * dim * vdim], a head's matrix after the other).  ``conv`` float32 rows hold
         q, k (kv_heads x dim) and v (heads x vdim) after convolution and SiLU from the columns ``offsets``;
         ``proj`` float32 rows hold the write-strength and decay projections (heads each) from ``gate_offsets``;
-        ``out`` float32 [T, heads * vdim]."""
+        ``out`` float32 [T, heads * vdim].  Single tokens: one kernel.  Prompt portions with ``plan``
+        (``plan_memory_chunks``, on the device), keys and values up to ``mlstm_chunk_max_dim`` and values a multiple
+        of 4: in chunks (a triangular system per chunk, a walk over each request's chunks, outputs in parallel);
+        other prompt portions: prepare + stream."""
         self._flush()
         self._load_recurrent()
         q_off, k_off, v_off = offsets
         b_off, a_off = gate_offsets
         tokens = conv.shape[0]
+        if (plan and tokens >= 8 * ctx.num_requests and max(dim, vdim) <= self.mlstm_chunk_max_dim and vdim % 4 == 0
+                and os.environ.get("CIE_RECURRENT_CHUNKS", "1") != "0"):
+            chunks = plan["chunk_row"].shape[0]
+            floats = int(self._gated_delta_chunk_floats(tokens, chunks, heads, dim, vdim))
+            rows = max(tokens, self.max_rows)
+            reserve = int(self._gated_delta_chunk_floats(rows, -(-rows // self.mlstm_chunk_tokens) + ctx.num_requests,
+                                                         heads, dim, vdim))
+            scratch = self.scratch(f"recurrent.delta_chunks.{heads}x{dim}x{vdim}", floats, reserve=max(floats, reserve))
+            self.launches += 4
+            self._gated_delta_chunked(_ptr(conv), conv.stride(0), q_off, k_off, v_off, _ptr(proj), proj.stride(0),
+                                      b_off, a_off, _ptr(a_log), _ptr(dt_bias), float(q_scale), _ptr(scratch), _ptr(out),
+                                      out.stride(0), _ptr(state), state.stride(0), _ptr(ctx.slots),
+                                      _ptr(ctx.request_active), _ptr(plan["chunk_row"]), _ptr(plan["chunk_count"]),
+                                      _ptr(plan["request_chunk_start"]), tokens, chunks, ctx.num_requests, heads,
+                                      kv_heads, dim, vdim, state.shape[0], _ptr(self.error_word), self.stream)
+            return
         if self._streams(tokens, ctx, dim):       # prompt portions: pack for all tokens at once, then stream
             packed = self._stream_scratch(tokens, heads, dim, vdim, False)
             self.launches += 2

@@ -51,6 +51,14 @@ class GatedDelta(Mixer):
                                            "dt_bias", "g", "norm", "o")}
         self.names.update(names or {})
 
+    @property
+    def plan_key(self):
+        return ("memory.chunks",)       # the matrix memory's chunks: one list serves both mixers
+
+    def plan(self, host, cache):
+        """Chunk work lists for a step with prompt portions."""
+        return self.runtime.ops.plan_memory_chunks(host)
+
     def state_spec(self) -> StateSpec:
         # the heads' matrices, then the convolution's history [taps - 1, channels]
         return StateSpec((self.matrix_floats + (self.taps - 1) * self.channels,), "float32")
@@ -101,7 +109,8 @@ class GatedDelta(Mixer):
         mixed = rt.workspace.get("gated_delta.o", tokens, vv, f32)
         ops.gated_delta_scan(conv, (0, qk, 2 * qk), proj, (self.channels + vv, self.channels + vv + heads),
                              self.a_log, self.dt_bias, self.key_dim ** -0.5, mixed, binding.state, ctx, heads,
-                             self.num_kv_heads, self.key_dim, self.value_dim)
+                             self.num_kv_heads, self.key_dim, self.value_dim,
+                             plan=getattr(ctx, "extras", {}).get(self.plan_key) or None)
         gated = rt.workspace.get("gated_delta.gated", tokens, vv, rt.dtype)
         ops.head_norm_gate(mixed, proj[:, self.channels:self.channels + vv], self.gain, self.eps, gated, heads,
                            gate_act="silu")

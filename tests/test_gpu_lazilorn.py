@@ -609,11 +609,12 @@ def test_short_convolution_reads_and_leaves_its_history(taps):
 
 @pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 2, 12, 20), (2, 1, 64, 128), (2, 2, 128, 64), (3, 1, 5, 130),
                                                    (1, 1, 160, 8)])
-@pytest.mark.parametrize("streams", ["1", "0"])
+@pytest.mark.parametrize("streams", ["chunks", "1", "0"])
 def test_gated_delta_rule_carries_its_state_between_steps(heads, groups, dim, vdim, streams, monkeypatch):
     """Three steps of unequal requests from states that are not zero; one request inactive in the second.
-    Prompt portions as prepare + stream (keys up to 128) or on the token-by-token kernel."""
-    monkeypatch.setenv("CIE_RECURRENT_STREAM", streams)
+    Prompt portions in chunks (keys and values up to 128, values a multiple of 4), as prepare + stream (keys up
+    to 128) or on the token-by-token kernel."""
+    monkeypatch.setenv("CIE_RECURRENT_STREAM", "0" if streams == "0" else "1")
     rt = runtime("float32")
     qk, vv = groups * dim, heads * vdim
     a_log, dt = rand(heads, scale=0.7, seed=1), rand(heads, scale=1.0, seed=2)
@@ -628,9 +629,16 @@ def test_gated_delta_rule_carries_its_state_between_steps(heads, groups, dim, vd
         gates = rand(tokens, 3 + 2 * heads, scale=2.0, seed=40 + step)
         ctx, starts = scan_ctx(lengths, slots, active)
         out = torch.empty(tokens, vv, dtype=torch.float32).cuda()
+        plan = None
+        if streams == "chunks":
+            plan = {name: torch.from_numpy(a).cuda() for name, a in rt.ops.plan_memory_chunks(ctx.host).items()}
+        before = rt.ops.launches
         rt.ops.gated_delta_scan(conv.cuda(), (0, qk, 2 * qk), gates.cuda(), (3, 3 + heads), a_log.cuda(), dt.cuda(),
-                                dim ** -0.5, out, state, ctx, heads, groups, dim, vdim)
+                                dim ** -0.5, out, state, ctx, heads, groups, dim, vdim, plan=plan)
         rt.ops.check_errors()
+        wide = tokens >= 8 * len(lengths)
+        chunked = streams == "chunks" and wide and max(dim, vdim) <= 128 and vdim % 4 == 0
+        assert rt.ops.launches - before == (4 if chunked else 2 if wide and streams != "0" and dim <= 128 else 1)
         for r in range(len(lengths)):
             rows, g = conv[starts[r]:starts[r + 1]].double(), gates[starts[r]:starts[r + 1]].double()
             q, k = rows[:, :qk].view(-1, groups, dim), rows[:, qk:2 * qk].view(-1, groups, dim)
