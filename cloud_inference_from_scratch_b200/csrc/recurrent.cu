@@ -575,7 +575,7 @@ recurrent_stream_kernel(const float* __restrict__ packed, float* __restrict__ ou
 // prompt portion can be cut into chunks of kMemChunk tokens that many CTAs work on at once.  With b_t the log
 // forget gates summed from the chunk's first token to t, m_t the running maximum (the recurrence above, taken
 // token by token so that it is the same number in every form) and m_c the maximum before the chunk:
-//   1. per token and head the two log gates; then per (request, head), a lane each: b_t, m_t, m_(t-1)
+//   1. per token and head the two log gates; then per (request, head), one warp: b_t, m_t, m_(t-1)
 //   2. per (chunk, head):               U = sum_s exp(b_last - b_s + i_s - m_last) k_s v_s^T, and the same with k_s alone
 //   3. per (request, head):             walks its chunks, S <- exp(b_last + m_c - m_last) S + U, leaving in U's place
 //                                       the state BEFORE the chunk; the last S, n and m go back to the slot
@@ -607,43 +607,49 @@ mlstm_gates_kernel(const float* __restrict__ proj, int proj_stride, int i_off, i
   *reinterpret_cast<float2*>(gates + (size_t)e * kMemGates) = make_float2(gi, gf);
 }
 
-// grid (requests, blocks of 32 heads); a lane a head.  The chain of a head is one addition and one maximum a
-// token; the gates of eight tokens are asked for together, ahead of the chain.
+// grid (requests, heads); one warp.  The chain of a head is one addition and one maximum a token: the warp brings
+// the gates of kWalkBlock tokens into shared memory, its first lane walks them there (the reads do not wait for the
+// chain), and the warp carries the results out.
+constexpr int kWalkBlock = 256;
 __global__ void __launch_bounds__(32)
 mlstm_gate_walk_kernel(const float* __restrict__ state, long long state_stride, float* __restrict__ gates,
                        const int* __restrict__ query_start, const int* __restrict__ slots, int heads, int dim, int vdim,
                        int max_slots, int* err) {
+  static_assert(kWalkBlock % kMemChunk == 0, "a block of the walk holds whole chunks");
+  __shared__ float2 in_s[kWalkBlock];
+  __shared__ __align__(16) float4 out_s[kWalkBlock];
   pdl_wait();
   pdl_trigger();
-  const int request = blockIdx.x, head = blockIdx.y * 32 + threadIdx.x;
+  const int request = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
   const int slot = slots[request];
   if (slot < 0 || slot >= max_slots) {
-    if (threadIdx.x == 0) atomicOr(err, kErrBadRequest);
+    if (lane == 0) atomicOr(err, kErrBadRequest);
     return;
   }
-  if (head >= heads) return;
   const int begin = query_start[request], end = query_start[request + 1];
   const int copies = (vdim + kNormaliserColumns - 1) / kNormaliserColumns;
   const size_t head_floats = (size_t)dim * vdim + (size_t)copies * (dim + 1);
   float m = state[(size_t)slot * state_stride + (size_t)head * head_floats + (size_t)dim * vdim + dim];
   float b = 0.f;
-  constexpr int kAhead = 8;
-  static_assert(kMemChunk % kAhead == 0, "a chunk starts at a multiple of the tokens taken together");
-  for (int t0 = begin; t0 < end; t0 += kAhead) {
-    float2 g[kAhead];
-#pragma unroll
-    for (int u = 0; u < kAhead; ++u)
-      g[u] = t0 + u < end ? *reinterpret_cast<const float2*>(gates + ((size_t)(t0 + u) * heads + head) * kMemGates)
-                          : make_float2(0.f, 0.f);
-    if ((t0 - begin) % kMemChunk == 0) b = 0.f;
-#pragma unroll
-    for (int u = 0; u < kAhead; ++u) {
-      if (t0 + u >= end) break;
-      b += g[u].y;
-      const float m_new = fmaxf(g[u].y + m, g[u].x);
-      *reinterpret_cast<float4*>(gates + ((size_t)(t0 + u) * heads + head) * kMemGates) = make_float4(g[u].x, b, m_new, m);
-      m = m_new;
+  for (int t0 = begin; t0 < end; t0 += kWalkBlock) {
+    const int n = min(kWalkBlock, end - t0);
+    for (int u = lane; u < n; u += 32)
+      in_s[u] = *reinterpret_cast<const float2*>(gates + ((size_t)(t0 + u) * heads + head) * kMemGates);
+    __syncwarp();
+    if (lane == 0) {
+#pragma unroll 8
+      for (int u = 0; u < n; ++u) {
+        const float2 g = in_s[u];
+        b = u % kMemChunk == 0 ? g.y : b + g.y;
+        const float m_new = fmaxf(g.y + m, g.x);
+        out_s[u] = make_float4(g.x, b, m_new, m);
+        m = m_new;
+      }
     }
+    __syncwarp();
+    for (int u = lane; u < n; u += 32)
+      *reinterpret_cast<float4*>(gates + ((size_t)(t0 + u) * heads + head) * kMemGates) = out_s[u];
+    __syncwarp();
   }
 }
 
@@ -933,6 +939,8 @@ chunk_output_kernel(RowsOf q_rows, RowsOf k_rows, RowsOf v_rows, float q_scale,
 // Ratios of decays are exponentials of differences of summed logarithms, never quotients.  Float32 on the CUDA cores.
 // Keys up to kMemDim, values a multiple of 4.
 constexpr int kWalkColumns = 32;
+constexpr int kWalkWarps = 16;                   // warps of the walk
+constexpr int kWalkRows = kMemDim / kWalkWarps;  // state rows of a warp
 
 // grid (chunks, heads).  packed: the prepared rows [k: P][q: P][gates][v: VP] per head and token.
 __global__ void __launch_bounds__(256)
@@ -1001,21 +1009,22 @@ delta_chunk_solve_kernel(const float* __restrict__ packed, int tokens, int row_f
   }
 }
 
-// grid (requests, heads, blocks of kWalkColumns value columns); 256 threads: warp w keeps state rows 16 w .. 16 w + 15
-// of the block's columns in registers, a lane a column.  What a chunk brings (W, k, U', the summed log decays) comes
+// grid (requests, heads, blocks of kWalkColumns value columns); warp w keeps kWalkRows state rows of the block's
+// columns in registers, a lane a column.  What a chunk brings (W, k, U', the summed log decays) comes
 // through two cp.async stages, a chunk ahead.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kWalkWarps * 32)
 delta_chunk_walk_kernel(const float* __restrict__ packed, int tokens, int row_floats, int P,
                         const float* __restrict__ gates, const float* __restrict__ w_in, float* __restrict__ u_io,
                         float* __restrict__ before, float* __restrict__ state, long long state_stride,
                         const int* __restrict__ request_chunk_start, const int* __restrict__ chunk_row,
                         const int* __restrict__ chunk_count, const int* __restrict__ slots,
                         const int* __restrict__ request_active, int heads, int dim, int vdim, int max_slots, int* err) {
-  constexpr int C = kMemChunk, kRows = kMemRows, kCols = kWalkColumns;
+  constexpr int C = kMemChunk, kRows = kWalkRows, kCols = kWalkColumns;
   extern __shared__ __align__(16) float smem[];
   const int stage_floats = 2 * C * P + C * kCols + C * kMemGates;
   float* part_s = smem + 2 * stage_floats;        // [warps][C][kCols]
-  float* u_s = part_s + kMemWarps * C * kCols;    // [C][kCols]
+  float* u_s = part_s + kWalkWarps * C * kCols;   // [C][kCols]
+  __shared__ float weight_s[C];
   pdl_wait();
   pdl_trigger();
   const int request = blockIdx.x, head = blockIdx.y, col0 = blockIdx.z * kCols, tid = threadIdx.x;
@@ -1083,7 +1092,8 @@ delta_chunk_walk_kernel(const float* __restrict__ packed, int tokens, int row_fl
       }
     }
     __syncthreads();
-    for (int t = warp; t < n; t += kMemWarps) {
+    if (tid < n) weight_s[tid] = expf(g_s[(n - 1) * kMemGates + 1] - g_s[tid * kMemGates + 1]);
+    for (int t = warp; t < n; t += kWalkWarps) {
       float u = ut_s[t * kCols + lane];
       for (int w = 0; w < warps; ++w) u -= part_s[(w * C + t) * kCols + lane];
       u_s[t * kCols + lane] = u;
@@ -1096,7 +1106,7 @@ delta_chunk_walk_kernel(const float* __restrict__ packed, int tokens, int row_fl
 #pragma unroll
       for (int r = 0; r < kRows; ++r) s[r] *= keep;
       for (int t = 0; t < n; ++t) {
-        const float u = u_s[t * kCols + lane] * expf(lg_last - g_s[t * kMemGates + 1]);
+        const float u = u_s[t * kCols + lane] * weight_s[t];
 #pragma unroll
         for (int r = 0; r < kRows; r += 4) {
           const float4 k4 = *reinterpret_cast<const float4*>(k_s + t * P + r0 + r);
@@ -1232,7 +1242,7 @@ extern "C" int cie_mlstm_chunked(const float* proj, int proj_stride, int q_off, 
   const dim3 grid(chunks, heads), block(kMemWarps * 32);
   CIE_LAUNCH("mlstm_gates", mlstm_gates_kernel, dim3((tokens * heads + 255) / 256), dim3(256), 0, s, proj, proj_stride,
              i_off, f_off, i_bias, f_bias, cap, gates, tokens, heads);
-  CIE_LAUNCH("mlstm_gate_walk", mlstm_gate_walk_kernel, dim3(requests, (heads + 31) / 32), dim3(32), 0, s,
+  CIE_LAUNCH("mlstm_gate_walk", mlstm_gate_walk_kernel, dim3(requests, heads), dim3(32), 0, s,
              (const float*)state, state_stride, gates, query_start, slots, heads, dim, vdim, max_slots, err);
   CIE_LAUNCH("mlstm_chunk_sums", mlstm_chunk_sums_kernel, grid, block, smem2, s, proj, proj_stride, k_off, v_off,
              (const float*)gates, sums, chunk_row, chunk_count, heads, dim, vdim);
@@ -1276,7 +1286,7 @@ extern "C" int cie_gated_delta_chunked(const float* conv, int conv_stride, int q
   float* before = u + (size_t)tokens * heads * vdim;
   const size_t smem2 = (size_t)(kMemChunk * (vdim + P + 1) + 2 * kMemChunk * (kMemChunk + 1)) * sizeof(float);
   const size_t smem3 = (size_t)(2 * (2 * kMemChunk * P + kMemChunk * kWalkColumns + kMemChunk * kMemGates) +
-                                (kMemWarps + 1) * kMemChunk * kWalkColumns) * sizeof(float);
+                                (kWalkWarps + 1) * kMemChunk * kWalkColumns) * sizeof(float);
   const size_t smem4 = (size_t)kMemChunk * (2 * dim + 1 + vdim + kMemChunk) * sizeof(float);
   if (cudaFuncSetAttribute(delta_chunk_solve_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2) != cudaSuccess ||
       cudaFuncSetAttribute(delta_chunk_walk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem3) != cudaSuccess ||
@@ -1289,7 +1299,7 @@ extern "C" int cie_gated_delta_chunked(const float* conv, int conv_stride, int q
   CIE_LAUNCH("delta_chunk_solve", delta_chunk_solve_kernel, grid, dim3(256), smem2, s, (const float*)packed, tokens,
              row_floats, P, gates, w, u, chunk_row, chunk_count, heads, vdim);
   CIE_LAUNCH("delta_chunk_walk", delta_chunk_walk_kernel, dim3(requests, heads, (vdim + kWalkColumns - 1) / kWalkColumns),
-             dim3(256), smem3, s, (const float*)packed, tokens, row_floats, P, (const float*)gates, (const float*)w, u,
+             dim3(kWalkWarps * 32), smem3, s, (const float*)packed, tokens, row_floats, P, (const float*)gates, (const float*)w, u,
              before, state, state_stride, request_chunk_start, chunk_row, chunk_count, slots, request_active, heads, dim,
              vdim, max_slots, err);
   const RowsOf q_rows{packed, (long long)tokens * row_floats, row_floats, P, 0};
