@@ -839,17 +839,40 @@ chunk_output_kernel(RowsOf q_rows, RowsOf k_rows, RowsOf v_rows, float q_scale,
   stage_rows(v_s, vdim, v_rows.base + head * v_rows.head_base, v_rows.stride, row0, n, v_rows.col0 + head * v_rows.head_col,
              vdim, [](int) { return 1.f; });
   __syncthreads();
-  for (int e = threadIdx.x; e < n * kMemChunk; e += blockDim.x) {
-    const int i = e / kMemChunk, j = e % kMemChunk;
-    float dot = 0.f;
-    if (j <= i) {
-      for (int x = 0; x < dim; ++x) dot = fmaf(q_s[i * dim + x], k_s[j * kd + x], dot);
-      dot *= expf(gb_s[i] - gb_s[j] + gi_s[j] - gm_s[i]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    // a warp takes four tokens that follow each other, a lane a key: a key's numbers are read once for four products
+    constexpr int kQ = kMemChunk / kMemWarps;
+    const int i0 = warp * kQ, j = lane;
+    float dot[kQ] = {};
+    if (i0 < n && j < n && j < i0 + kQ) {
+      const int whole = dim % 4 == 0 ? dim : 0;
+      for (int x = 0; x < whole; x += 4) {
+        const float k0 = k_s[j * kd + x], k1 = k_s[j * kd + x + 1], k2 = k_s[j * kd + x + 2], k3 = k_s[j * kd + x + 3];
+#pragma unroll
+        for (int t = 0; t < kQ; ++t) {
+          if (i0 + t >= n) break;
+          const float4 q4 = *reinterpret_cast<const float4*>(q_s + (i0 + t) * dim + x);
+          dot[t] = fmaf(q4.x, k0, dot[t]);
+          dot[t] = fmaf(q4.y, k1, dot[t]);
+          dot[t] = fmaf(q4.z, k2, dot[t]);
+          dot[t] = fmaf(q4.w, k3, dot[t]);
+        }
+      }
+      for (int x = whole; x < dim; ++x) {
+        const float kx = k_s[j * kd + x];
+#pragma unroll
+        for (int t = 0; t < kQ; ++t)
+          if (i0 + t < n) dot[t] = fmaf(q_s[(i0 + t) * dim + x], kx, dot[t]);
+      }
     }
-    a_s[e] = dot;
+#pragma unroll
+    for (int t = 0; t < kQ; ++t) {
+      const int i = i0 + t;
+      a_s[i * kMemChunk + j] = (i < n && j <= i) ? dot[t] * expf(gb_s[i] - gb_s[j] + gi_s[j] - gm_s[i]) : 0.f;
+    }
   }
   __syncthreads();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const size_t cells = (size_t)dim * vdim + (kMemory ? dim : 0);
   const float* before = chunk_sums + ((size_t)chunk * heads + head) * cells;
   const float* n_before = before + (size_t)dim * vdim;
@@ -972,14 +995,23 @@ delta_chunk_solve_kernel(const float* __restrict__ packed, int tokens, int row_f
   stage_rows(k_s, kd, rows, row_floats, row0, n, 0, P, [](int) { return 1.f; });
   stage_rows(v_s, vdim, rows, row_floats, row0, n, 2 * P + kStreamGates, vdim, [](int) { return 1.f; });
   __syncthreads();
-  for (int e = tid; e < C * C; e += blockDim.x) {
-    const int t = e / C, j = e % C;
-    float a = 0.f;
-    if (j < t && t < n) {
-      for (int x = 0; x < P; ++x) a = fmaf(k_s[t * kd + x], k_s[j * kd + x], a);
-      a *= beta_s[t] * expf(lg_s[t] - lg_s[j]);
+  {
+    // a warp takes four tokens that follow each other, a lane an earlier token
+    constexpr int kQ = C / 8;
+    const int t0 = (tid >> 5) * kQ, j = tid & 31;
+    float a[kQ] = {};
+    if (t0 < n && j < t0 + kQ - 1 && j < n) {
+      for (int x = 0; x < P; ++x) {
+        const float kx = k_s[j * kd + x];
+#pragma unroll
+        for (int t = 0; t < kQ; ++t) a[t] = fmaf(k_s[(t0 + t) * kd + x], kx, a[t]);
+      }
     }
-    a_s[t * (C + 1) + j] = a;
+#pragma unroll
+    for (int t = 0; t < kQ; ++t) {
+      const int row = t0 + t;
+      a_s[row * (C + 1) + j] = (j < row && row < n) ? a[t] * beta_s[row] * expf(lg_s[row] - lg_s[j]) : 0.f;
+    }
   }
   __syncthreads();
   if (tid < C) {            // column tid of T = (I + A)^-1: T_tj = [t = j] - sum_(s<t) A_ts T_sj
