@@ -490,7 +490,8 @@ def memory_gates(rows_i, rows_f, bias_i, bias_f, cap):
 
 
 @pytest.mark.parametrize("heads,dim,vdim,cap", [(3, 20, 36, 9.0), (2, 64, 64, 15.0), (1, 128, 32, 4.0), (2, 5, 130, 1.0),
-                                                (2, 160, 8, 30.0), (1, 64, 300, 9.0), (2, 200, 136, 9.0)])
+                                                (2, 160, 8, 30.0), (1, 64, 300, 9.0), (2, 200, 136, 9.0), (2, 6, 30, 9.0),
+                                                (1, 7, 127, 12.0)])
 @pytest.mark.parametrize("streams", ["chunks", "1", "0"])
 def test_matrix_memory_carries_matrix_normaliser_and_maximum_between_steps(heads, dim, vdim, cap, streams, monkeypatch):
     """Prompt portions in chunks (keys and values up to 128), as prepare + stream (keys up to 128) or on the
@@ -608,7 +609,7 @@ def test_short_convolution_reads_and_leaves_its_history(taps):
 
 
 @pytest.mark.parametrize("heads,groups,dim,vdim", [(4, 2, 12, 20), (2, 1, 64, 128), (2, 2, 128, 64), (3, 1, 5, 130),
-                                                   (1, 1, 160, 8)])
+                                                   (1, 1, 160, 8), (2, 2, 10, 36), (2, 1, 33, 30)])
 @pytest.mark.parametrize("streams", ["chunks", "1", "0"])
 def test_gated_delta_rule_carries_its_state_between_steps(heads, groups, dim, vdim, streams, monkeypatch):
     """Three steps of unequal requests from states that are not zero; one request inactive in the second.
