@@ -20,7 +20,9 @@
 // Both scans: a block per (request, head, block of value columns); eight lanes share a value column, each
 // keeps an eighth of its rows in registers, and their sums meet by shuffles.  The rows a token brings are
 // staged in shared memory one token ahead.  Everything is float32.  A request's result depends on its own
-// tokens and state only, whatever the batch, the cut of a prompt into portions, or the slot.
+// tokens and state only, whatever the batch, the cut of a prompt into portions, or the slot (beyond the order of
+// additions: prompt portions run in chunks of 32 tokens where the head sizes allow, else as a prepare kernel and
+// a stream kernel with a thread a value column; the sections further down say how).
 //
 // A last kernel divides every head of a scan's output by its own root mean square, multiplies by a gain
 // (one number per column, or a vector of a head's size shared by the heads) and by sigmoid or SiLU of a
