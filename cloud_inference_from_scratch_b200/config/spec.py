@@ -90,11 +90,14 @@ class ScheduleEntry:
     ``entry_offset``  (tensor name, row): row ``row`` of the stored tensor [rows, hidden] is
                    added to the residual stream of every token right before this run (a
                    learned offset per pass of a looped run of layers).
+    ``adds_embedding``  the embedding rows (the stream as it was before the first layer) are added to the
+                   stream once more right before this run.
     """
 
     layer: int
     reads_cache_of: int | None = None
     entry_offset: tuple[str, int] | None = None
+    adds_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -125,6 +128,9 @@ class ModelSpec:
     position_wave_base: float | None = None
     # rows of each tensor that a schedule entry names as its ``entry_offset``
     offset_tensors: tuple[tuple[str, int], ...] = ()
+    # every sublayer's result is multiplied by this constant as it is added to the stream (the norms of such a
+    # model are built with the same constant as their ``update_scale``)
+    residual_scale: float = 1.0
 
     def validate(self) -> None:
         if not self.layers:
@@ -143,6 +149,8 @@ class ModelSpec:
                     raise ValueError(f"schedule entry {index} adds row {row} of {name!r}, which offset_tensors does not have")
                 if self.residual_streams != 1:
                     raise ValueError("entry offsets are built for one residual stream")
+            if entry.adds_embedding and self.residual_streams != 1:
+                raise ValueError("adding the embedding rows again is built for one residual stream")
         for index, entry in enumerate(self.schedule):
             if not 0 <= entry.layer < len(self.layers):
                 raise ValueError(f"schedule entry {index} names layer {entry.layer}, which does not exist")

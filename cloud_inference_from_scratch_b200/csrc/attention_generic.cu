@@ -16,6 +16,9 @@
 // `keep_first` > 0 (with a window): the first keep_first keys of the request stay visible after the
 // window has moved past them; the visible keys are then 0..keep_first-1 and p-window+1..p, visited in
 // that order as one list.
+//
+// `sinks` != nullptr: the softmax denominator of query head h holds one more term exp(sinks[h]), which has no
+// key and no value and is not scaled.
 #include "common.cuh"
 
 #include <cfloat>
@@ -34,7 +37,8 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
                          const int* __restrict__ positions, const int* __restrict__ request_of_token,
                          const int* __restrict__ table, int table_width, int num_pages, int tokens,
                          int q_heads, int kv_heads, int dim, int vdim, int page_size, float scale, int window,
-                         int keep_first, const float* __restrict__ r1, const float* __restrict__ r2, int* err) {
+                         int keep_first, const float* __restrict__ r1, const float* __restrict__ r2,
+                         const float* __restrict__ sinks, int* err) {
   __shared__ float q_s[kWarps][kMaxDim];
   __shared__ float p_s[kWarps][32];
   __shared__ long long off_s[kWarps][32];
@@ -112,7 +116,13 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ 
     __syncwarp();
   }
   T* o = out + (size_t)t * out_stride + (size_t)h * vdim;
-  const float inv = l > 0.f ? 1.f / l : 0.f;
+  float keep = 1.f;
+  if (sinks) {      // the sink joins the denominator, measured from the larger of the two maxima
+    const float top = fmaxf(m, sinks[h]);
+    keep = expf(m - top);
+    l = l * keep + expf(sinks[h] - top);
+  }
+  const float inv = l > 0.f ? keep / l : 0.f;
 #pragma unroll
   for (int i = 0; i < kMaxDim / 32; ++i) {
     const int d = lane + 32 * i;
@@ -152,7 +162,8 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
                        const int* __restrict__ positions, const int* __restrict__ request_of_token,
                        const int* __restrict__ table, int table_width, int num_pages, int q_heads,
                        int kv_heads, int dim, int vdim, int page_size, float scale, int window, int keep_first,
-                       const float* __restrict__ r1, const float* __restrict__ r2, int splits,
+                       const float* __restrict__ r1, const float* __restrict__ r2,
+                       const float* __restrict__ sinks, int splits,
                        float* __restrict__ shares, int* __restrict__ tickets, int* err) {
   // splits > 1: the keys of a token are cut into that many ranges, one CTA each (blockIdx.x = token *
   // splits + range); a CTA leaves its maximum, sum and unnormalised output in `shares`, and whoever
@@ -293,10 +304,12 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
   float* my_share = shares ? shares + (unit * splits + split) * kGroupHeads * kShare : nullptr;
   for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) {
     const int h = e / vdim, d = e % vdim;
-    float top = -FLT_MAX;
+    const bool sunk = sinks != nullptr && splits == 1;     // with key ranges the sink joins when they are joined
+    const float sink = sunk ? sinks[kvh * group + h0 + h] : -FLT_MAX;
+    float top = sink;
 #pragma unroll
     for (int w = 0; w < kGroupWarps; ++w) top = fmaxf(top, ml_s[(w * kGroupHeads + h) * 2]);
-    float sum = 0.f, value = 0.f;
+    float sum = sunk ? expf(sink - top) : 0.f, value = 0.f;
 #pragma unroll
     for (int w = 0; w < kGroupWarps; ++w) {
       const float share = expf(ml_s[(w * kGroupHeads + h) * 2] - top);
@@ -328,9 +341,10 @@ attention_group_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ ou
   const float* unit_shares = shares + unit * splits * kGroupHeads * kShare;
   for (int e = threadIdx.x; e < heads * vdim; e += blockDim.x) {
     const int h = e / vdim, d = e % vdim;
-    float top = -FLT_MAX;
+    const float sink = sinks ? sinks[kvh * group + h0 + h] : -FLT_MAX;
+    float top = sink;
     for (int r = 0; r < splits; ++r) top = fmaxf(top, __ldcg(unit_shares + (r * kGroupHeads + h) * kShare + kGroupMaxV));
-    float sum = 0.f, value = 0.f;
+    float sum = sinks ? expf(sink - top) : 0.f, value = 0.f;
     for (int r = 0; r < splits; ++r) {
       const float* part = unit_shares + (r * kGroupHeads + h) * kShare;
       const float share = expf(__ldcg(part + kGroupMaxV) - top);
@@ -353,13 +367,15 @@ extern "C" int cie_attention_group_share_floats() { return kGroupHeads * (kGroup
 // keys are cut into that many ranges with a CTA each; `shares` holds tokens * kv_heads *
 // ceil(group / 8) * splits * cie_attention_group_share_floats() floats and `tickets` one int, zero, per
 // (token, kv head, 8 heads).
-extern "C" int cie_attention_generic_split(const void* q, int q_stride, void* out, int out_stride,
-                                           const void* k_pool, const void* v_pool, const int* positions,
-                                           const int* request_of_token, const int* table, int table_width,
-                                           int num_pages, int tokens, int q_heads, int kv_heads, int dim,
-                                           int vdim, int page_size, float scale, int window,
-                                           const float* r1, const float* r2, int splits, float* shares,
-                                           int* tickets, int keep_first, int dtype, int* err, void* stream) {
+// sinks: float32 [q_heads] or nullptr.
+extern "C" int cie_attention_generic_sink(const void* q, int q_stride, void* out, int out_stride,
+                                          const void* k_pool, const void* v_pool, const int* positions,
+                                          const int* request_of_token, const int* table, int table_width,
+                                          int num_pages, int tokens, int q_heads, int kv_heads, int dim,
+                                          int vdim, int page_size, float scale, int window,
+                                          const float* r1, const float* r2, int splits, float* shares,
+                                          int* tickets, int keep_first, const float* sinks, int dtype, int* err,
+                                          void* stream) {
   if (tokens <= 0) return 0;
   if (keep_first < 0) CIE_FAIL("attention_generic: %d kept keys", keep_first);
   if (splits < 1 || (splits > 1 && (!shares || !tickets))) CIE_FAIL("attention_generic: %d key ranges need shares and tickets", splits);
@@ -391,7 +407,7 @@ extern "C" int cie_attention_generic_split(const void* q, int q_stride, void* ou
     CIE_LAUNCH("attention_group", (attention_group_kernel<T, S>), grid, dim3(kGroupWarps * 32), smem, s,            \
                (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pool, (const T*)v_pool, positions,          \
                request_of_token, table, table_width, num_pages, q_heads, kv_heads, dim, vdim, page_size, scale,    \
-               window, keep_first, r1, r2, splits, shares, tickets, err);                                          \
+               window, keep_first, r1, r2, sinks, splits, shares, tickets, err);                                   \
   } while (0)
     if (dtype == kFloat32) CIE_GROUP(float, false);
     else if (staged) CIE_GROUP(__nv_bfloat16, true);
@@ -403,16 +419,29 @@ extern "C" int cie_attention_generic_split(const void* q, int q_stride, void* ou
     CIE_LAUNCH("attention_generic", attention_generic_kernel<float>, dim3(blocks), dim3(kWarps * 32), 0, s,
         (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_pool, (const float*)v_pool,
         positions, request_of_token, table, table_width, num_pages, tokens, q_heads, kv_heads, dim, vdim,
-        page_size, scale, window, keep_first, r1, r2, err);
+        page_size, scale, window, keep_first, r1, r2, sinks, err);
   } else if (dtype == kBFloat16) {
     CIE_LAUNCH("attention_generic", attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(kWarps * 32), 0, s,
         (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
         (const __nv_bfloat16*)v_pool, positions, request_of_token, table, table_width, num_pages, tokens,
-        q_heads, kv_heads, dim, vdim, page_size, scale, window, keep_first, r1, r2, err);
+        q_heads, kv_heads, dim, vdim, page_size, scale, window, keep_first, r1, r2, sinks, err);
   } else {
     CIE_FAIL("attention_generic: unknown element type code %d", dtype);
   }
   return 0;
+}
+
+extern "C" int cie_attention_generic_split(const void* q, int q_stride, void* out, int out_stride,
+                                           const void* k_pool, const void* v_pool, const int* positions,
+                                           const int* request_of_token, const int* table, int table_width,
+                                           int num_pages, int tokens, int q_heads, int kv_heads, int dim,
+                                           int vdim, int page_size, float scale, int window,
+                                           const float* r1, const float* r2, int splits, float* shares,
+                                           int* tickets, int keep_first, int dtype, int* err, void* stream) {
+  return cie_attention_generic_sink(q, q_stride, out, out_stride, k_pool, v_pool, positions, request_of_token,
+                                    table, table_width, num_pages, tokens, q_heads, kv_heads, dim, vdim,
+                                    page_size, scale, window, r1, r2, splits, shares, tickets, keep_first, nullptr,
+                                    dtype, err, stream);
 }
 
 extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, int out_stride,

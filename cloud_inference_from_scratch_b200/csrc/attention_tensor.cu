@@ -63,6 +63,9 @@ struct PrefillArgs {
   const float* r1;
   const float* r2;
   int split_weights;   // the softmax weights enter the value product as two bfloat16 terms each
+  // one more term exp(sinks[h]) in the softmax denominator of query head h (no key, no value, not scaled);
+  // nullptr: none
+  const float* sinks;
 };
 
 // One 64-key tile: thread t < 64 copies key row t of K, thread 64 + t row t of V, each with one bulk
@@ -208,10 +211,17 @@ __global__ void __launch_bounds__(PREFILL_WARPS * 32) prefill_kernel(const Prefi
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     if (row_pos[h] < 0) continue;
-    const float total = quad_sum(l[h]);
-    const float inv = total > 0.f ? 1.f / total : 0.f;
+    float total = quad_sum(l[h]);
     const int r = warp * 16 + g + h * 8;
     const int tok = r / a.hpt, hh = h0 + r % a.hpt;
+    float keep = 1.f;
+    if (a.sinks) {      // maxima are kept in units of log 2
+      const float sink = a.sinks[kvh * a.group + hh] * 1.4426950408889634f;
+      const float top = fmaxf(m[h], sink);
+      keep = exp2f(m[h] - top);
+      total = total * keep + exp2f(sink - top);
+    }
+    const float inv = total > 0.f ? keep / total : 0.f;
     bf16* dst = a.out + (size_t)(first_token + tok) * a.out_stride + (size_t)(kvh * a.group + hh) * D;
 #pragma unroll
     for (int i = 0; i < NTILES_D; ++i) {
@@ -1146,7 +1156,7 @@ extern "C" int cie_attention_head_dim() { return D; }
 
 // r1, r2: float32 [q_heads] of the distance penalty, or both null; split_weights: 1 keeps the
 // softmax weights to 16 bits of mantissa in the value product (two bfloat16 terms); keep_first: with a window,
-// the request's first so many keys stay visible behind it.
+// the request's first so many keys stay visible behind it; sinks: float32 [q_heads] or null.
 extern "C" int cie_attention_prefill_ex(const void* q, int q_stride, void* out, int out_stride,
                                         const void* k_pool, const void* v_pool, const int* table,
                                         int table_width, int num_pages, const int* tile_request,
@@ -1154,7 +1164,7 @@ extern "C" int cie_attention_prefill_ex(const void* q, int q_stride, void* out, 
                                         const int* query_lens, const int* query_start, int q_heads,
                                         int kv_heads, int page_size, int hpt, float scale, int window,
                                         const float* r1, const float* r2, int split_weights, int keep_first,
-                                        int* err, void* stream) {
+                                        const float* sinks, int* err, void* stream) {
   if (num_tiles <= 0) return 0;
   if (keep_first < 0) CIE_FAIL("attention_prefill: %d kept first keys", keep_first);
   if ((r1 == nullptr) != (r2 == nullptr)) CIE_FAIL("attention_prefill: the distance penalty needs both of its vectors");
@@ -1169,7 +1179,7 @@ extern "C" int cie_attention_prefill_ex(const void* q, int q_stride, void* out, 
   a.query_lens = query_lens; a.query_start = query_start;
   a.group = group; a.hpt = hpt; a.tpt = BM / hpt; a.head_chunks = (group + hpt - 1) / hpt;
   a.scale_log2 = scale * kLog2e; a.window = window; a.keep_first = window > 0 ? keep_first : 0; a.err = err;
-  a.r1 = r1; a.r2 = r2; a.split_weights = split_weights;
+  a.r1 = r1; a.r2 = r2; a.split_weights = split_weights; a.sinks = sinks;
   const size_t smem = (size_t)(BM + 4 * BN) * ROW * sizeof(bf16);
   static bool configured = false;
   if (!configured) {
@@ -1191,8 +1201,8 @@ extern "C" int cie_attention_prefill(const void* q, int q_stride, void* out, int
                                      int* err, void* stream) {
   return cie_attention_prefill_ex(q, q_stride, out, out_stride, k_pool, v_pool, table, table_width, num_pages,
                                   tile_request, tile_q0, num_tiles, context_lens, query_lens, query_start,
-                                  q_heads, kv_heads, page_size, hpt, scale, window, nullptr, nullptr, 0, 0, err,
-                                  stream);
+                                  q_heads, kv_heads, page_size, hpt, scale, window, nullptr, nullptr, 0, 0, nullptr,
+                                  err, stream);
 }
 
 // splits: CTAs that share the keys of one request (a thread-block cluster): 1, 2, 4 or 8.

@@ -177,6 +177,84 @@ __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ residual, const __
   *reinterpret_cast<uint4*>(out + (size_t)r * hidden + i) = packed;
 }
 
+// ---------------------------------------------------------------- residual add + layer norm
+// One block per output row, as above, for the norm with gain and bias:
+// out = gain * (x - mean(x)) * rsqrt(mean((x - mean(x))^2) + eps) + bias, x = residual + update_scale * update.
+// The update is one tensor of the activation type or float32 terms [splits][rows][hidden] (added in ascending
+// order, then scaled once).  The row stays in registers (up to kNormPerThread * blockDim elements) or is read
+// again; the mean is taken first and the variance from the deviations, all float32.
+template <typename T>
+__global__ void add_layernorm_kernel(float* __restrict__ residual, const void* __restrict__ update,
+                                     int partial_splits, size_t partial_stride, float update_scale,
+                                     const float* __restrict__ gain, const float* __restrict__ bias,
+                                     T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();   // see add_rmsnorm_kernel
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * hidden;
+  const bool has_update = update != nullptr;
+  const T* upd = (has_update && partial_splits == 0) ? reinterpret_cast<const T*>(update) + (size_t)src * hidden : nullptr;
+  const float* part = (has_update && partial_splits > 0) ? reinterpret_cast<const float*>(update) + (size_t)src * hidden : nullptr;
+  const bool write_back = (rows == nullptr) && has_update;
+  auto value = [&](int i) {
+    float x = res[i];
+    if (upd) x = fmaf(update_scale, to_float(upd[i]), x);
+    if (part) x = fmaf(update_scale, sum_partials(part + i, partial_splits, partial_stride), x);
+    return x;
+  };
+  T* dst = out + (size_t)r * hidden;
+  const float count = (float)hidden;
+  if (hidden <= kNormPerThread * (int)blockDim.x) {
+    float x[kNormPerThread];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kNormPerThread; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      x[j] = i < hidden ? value(i) : 0.f;
+      sum += x[j];
+    }
+    const float mean = block_sum(sum, scratch) / count;
+    __syncthreads();     // the scratch of the first sum is read before the second writes it
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < kNormPerThread; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      const float d = i < hidden ? x[j] - mean : 0.f;
+      sq = fmaf(d, d, sq);
+    }
+    const float inv = rsqrtf(block_sum(sq, scratch) / count + eps);
+#pragma unroll
+    for (int j = 0; j < kNormPerThread; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < hidden) {
+        if (write_back) res[i] = x[j];
+        dst[i] = from_float<T>(fmaf(gain[i], (x[j] - mean) * inv, bias ? bias[i] : 0.f));
+      }
+    }
+    return;
+  }
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float x = value(i);
+    if (write_back) res[i] = x;
+    sum += x;
+  }
+  const float mean = block_sum(sum, scratch) / count;
+  __syncthreads();
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float d = (write_back ? res[i] : value(i)) - mean;
+    sq = fmaf(d, d, sq);
+  }
+  const float inv = rsqrtf(block_sum(sq, scratch) / count + eps);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float x = write_back ? res[i] : value(i);
+    dst[i] = from_float<T>(fmaf(gain[i], (x - mean) * inv, bias ? bias[i] : 0.f));
+  }
+}
+
 // ---------------------------------------------------------------- rotary + paged KV write
 // qkv: [T, (Hq + 2 Hkv) * D], q heads first, then k heads, then v heads.  q is rotated in place.
 // k is rotated and written, v is copied, to pool[page][kv_head][pos % page][D] with
@@ -509,6 +587,29 @@ __global__ void gated_act_kernel(const TI* __restrict__ gate_up, const float* __
   }
 }
 
+// ---------------------------------------------------------------- act(gate) * up
+// gate_up: [tokens][2 * inter] = [gate | up], float32 or the activation type; out = act(gate) * up in float32,
+// rounded once.  kind 0: SiLU; kind 1: the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))).
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+  const float inner = 0.7978845608028654f * fmaf(0.044715f * z * z, z, z);
+  return 0.5f * z * (1.f + tanhf(inner));
+}
+
+template <typename TI, typename T>
+__global__ void glu_act_kernel(const TI* __restrict__ gate_up, T* __restrict__ out, int tokens, int inter, int kind) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t total = (size_t)tokens * inter;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / inter;
+    const int c = (int)(i % inter);
+    const float g = to_float(gate_up[t * 2 * inter + c]);
+    const float u = to_float(gate_up[t * 2 * inter + inter + c]);
+    const float a = kind == 1 ? gelu_tanh_f(g) : g / (1.f + expf(-g));
+    out[i] = from_float<T>(a * u);
+  }
+}
+
 // ---------------------------------------------------------------- embedding + sinusoid of the position
 // residual[t] = table[ids[t]] * scale + wave(positions[t]): entry 2i of the wave is sin(p * freq[i]), entry
 // 2i + 1 is cos(p * freq[i]); `freq` holds ceil(hidden / 2) float32 frequencies (rounded once from double on
@@ -537,16 +638,21 @@ __global__ void embedding_wave_kernel(const int* __restrict__ ids, const int* __
 }
 
 // ---------------------------------------------------------------- a vector added to every row of the stream
-// residual[t][i] += vec[i] (+ the pending update: float32 terms [splits][rows][hidden] `stride` apart, added in
-// ascending order).  What a run of layers that starts with a learned offset does before its first norm.
+// residual[t][i] += vec[i] + base[t][i] + scale * (the pending update: float32 terms [splits][rows][hidden]
+// `stride` apart, added in ascending order); `vec`, `base` and the update may each be absent.  What a run of
+// layers that starts with a learned offset (and, in a later pass of a looped run, the embedding rows once
+// more) does before its first norm.
 __global__ void add_rows_kernel(float* __restrict__ residual, const float* __restrict__ update, int splits,
-                                size_t stride, const float* __restrict__ vec, int hidden, size_t total) {
+                                size_t stride, float scale, const float* __restrict__ base,
+                                const float* __restrict__ vec, int hidden, size_t total) {
   pdl_wait();
   pdl_trigger();
   for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
     float x = residual[e];
-    if (update) x += sum_partials(update + e, splits, stride);
-    residual[e] = x + vec[e % hidden];
+    if (update) x = fmaf(scale, sum_partials(update + e, splits, stride), x);
+    if (base) x += base[e];
+    if (vec) x += vec[e % hidden];
+    residual[e] = x;
   }
 }
 
@@ -627,13 +733,13 @@ extern "C" int cie_embedding_wave(const int* ids, const int* positions, const vo
   return 0;
 }
 
-extern "C" int cie_add_rows(float* residual, const float* update, int splits, long long stride, const float* vec,
-                            int tokens, int hidden, void* stream) {
+extern "C" int cie_add_rows(float* residual, const float* update, int splits, long long stride, float scale,
+                            const float* base, const float* vec, int tokens, int hidden, void* stream) {
   if (tokens <= 0) return 0;
   if (update && (splits < 1 || splits > kMaxSplits)) CIE_FAIL("add_rows: %d terms of an update", splits);
   const size_t total = (size_t)tokens * hidden;
   CIE_LAUNCH("add_rows", add_rows_kernel, dim3(blocks_for(total)), dim3(256), 0, (cudaStream_t)stream, residual,
-             update, splits, (size_t)stride, vec, hidden, total);
+             update, splits, (size_t)stride, scale, base, vec, hidden, total);
   return 0;
 }
 
@@ -692,6 +798,41 @@ extern "C" int cie_add_rmsnorm(float* residual, const void* update, int partial_
     CIE_LAUNCH("add_rmsnorm", add_rmsnorm_kernel<T>, dim3(count), dim3(threads_for(hidden / 4)), 0,
                (cudaStream_t)stream, residual, update, partial_splits, (size_t)partial_stride,
                update_bias, gain, (T*)out, rows, hidden, eps);
+  })
+  return 0;
+}
+
+extern "C" int cie_add_layernorm(float* residual, const void* update, int partial_splits,
+                                 long long partial_stride, float update_scale, const float* gain,
+                                 const float* bias, void* out, const int* rows, int count, int hidden,
+                                 float eps, int dtype, void* stream) {
+  if (count <= 0) return 0;
+  if (partial_splits > kMaxSplits) CIE_FAIL("add_layernorm: at most %d float32 terms, got %d", kMaxSplits, partial_splits);
+  DISPATCH_DTYPE(dtype, "add_layernorm", {
+    CIE_LAUNCH("add_layernorm", add_layernorm_kernel<T>, dim3(count), dim3(threads_for(hidden / 4)), 0,
+               (cudaStream_t)stream, residual, update, partial_splits, (size_t)partial_stride, update_scale,
+               gain, bias, (T*)out, rows, hidden, eps);
+  })
+  return 0;
+}
+
+extern "C" int cie_glu_act(const void* gate_up, int in_dtype, void* out, int tokens, int inter, int kind,
+                           int dtype, void* stream) {
+  if (tokens <= 0) return 0;
+  if (kind < 0 || kind > 1) CIE_FAIL("glu_act: unknown activation %d", kind);
+  const size_t total = (size_t)tokens * inter;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  DISPATCH_DTYPE(dtype, "glu_act", {
+    if (in_dtype == kFloat32) {
+      CIE_LAUNCH("glu_act", (glu_act_kernel<float, T>), dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
+                 (const float*)gate_up, (T*)out, tokens, inter, kind);
+    } else if (in_dtype == dtype) {
+      CIE_LAUNCH("glu_act", (glu_act_kernel<T, T>), dim3(blocks), dim3(256), 0, (cudaStream_t)stream,
+                 (const T*)gate_up, (T*)out, tokens, inter, kind);
+    } else {
+      CIE_FAIL("glu_act: input type code %d with output type code %d", in_dtype, dtype);
+    }
   })
   return 0;
 }

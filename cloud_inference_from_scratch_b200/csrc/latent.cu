@@ -265,7 +265,7 @@ latent_attention_kernel(const float* __restrict__ q_abs, const float* __restrict
                         const int* __restrict__ table, int table_width, int num_pages,
                         const float* __restrict__ inv_freq, float magnitude, int interleaved, int rot_dims,
                         const float* __restrict__ sink, int heads, int rank, int rot, int page_size, float scale,
-                        int range_keys, int ranges, int* err) {
+                        int range_keys, int ranges, int window, int* err) {
   extern __shared__ __align__(16) float shared[];
   const int D = rank + rot;
   const int ld = (int)latent_row_floats(rank, rot);
@@ -281,7 +281,9 @@ latent_attention_kernel(const float* __restrict__ q_abs, const float* __restrict
   const bool live = h < heads;
   const int pos = positions[t];
   const int length = pos + 1;
-  const int begin = blockIdx.z * range_keys;
+  // window > 0: the token sees its last `window` keys (itself included); ranges count from the first of them
+  const int first = (window > 0 && length > window) ? length - window : 0;
+  const int begin = first + blockIdx.z * range_keys;
   if (begin >= length) return;
   const int end = min(length, begin + range_keys);
   const int* pages = table + (size_t)request_of_token[t] * table_width;
@@ -389,13 +391,14 @@ latent_attention_kernel(const float* __restrict__ q_abs, const float* __restrict
 // Joins the key ranges of every (token, head): grid (tokens, heads), in ascending range order.
 __global__ void __launch_bounds__(128)
 latent_merge_kernel(const float* __restrict__ part, float* __restrict__ out, const int* __restrict__ positions,
-                    const float* __restrict__ sink, int heads, int rank, int range_keys, int ranges) {
+                    const float* __restrict__ sink, int heads, int rank, int range_keys, int ranges, int window) {
   constexpr int kHeld = 256;          // weights of this many ranges are worked out once and kept
   __shared__ float held[kHeld];
   pdl_wait();
   pdl_trigger();
   const int t = blockIdx.x, h = blockIdx.y;
-  const int used = min(ranges, (positions[t] + range_keys) / range_keys);   // ceil((pos + 1) / range_keys)
+  const int seen = window > 0 ? min(positions[t] + 1, window) : positions[t] + 1;      // visible keys
+  const int used = min(ranges, (seen + range_keys - 1) / range_keys);
   const float* share = part + ((size_t)t * heads + h) * ranges * (rank + 2);
   float top = sink ? sink[h] : -FLT_MAX;
   for (int r = 0; r < used; ++r) top = fmaxf(top, share[(size_t)r * (rank + 2)]);
@@ -487,11 +490,11 @@ extern "C" int cie_head_scatter(const void* y, void* out, int out_stride, int ou
 }
 
 extern "C" int cie_latent_merge(const float* part, float* out, const int* positions, const float* sink, int tokens,
-                                int heads, int rank, int range_keys, int ranges, void* stream) {
+                                int heads, int rank, int range_keys, int ranges, int window, void* stream) {
   using namespace cie;
   if (tokens <= 0) return 0;
   CIE_LAUNCH("latent_merge", latent_merge_kernel, dim3(tokens, heads), dim3(128), 0, (cudaStream_t)stream, part, out,
-             positions, sink, heads, rank, range_keys, ranges);
+             positions, sink, heads, rank, range_keys, ranges, window);
   return 0;
 }
 
@@ -503,7 +506,7 @@ extern "C" int cie_latent_attention(const float* q_abs, const float* q_raw, int 
                                     int table_width, int num_pages, const float* inv_freq, float magnitude,
                                     int interleaved, int rot_dims, const float* sink, int tokens, int heads,
                                     int rank, int rot, int page_size, float scale, int range_keys, int ranges,
-                                    int dtype, int* err, void* stream) {
+                                    int window, int dtype, int* err, void* stream) {
   using namespace cie;
   if (tokens <= 0) return 0;
   if (rank > kLatentMaxRank) CIE_FAIL("latent_attention: latent size %d is above %d", rank, kLatentMaxRank);
@@ -524,10 +527,10 @@ extern "C" int cie_latent_attention(const float* q_abs, const float* q_raw, int 
     CIE_LAUNCH("latent_attention", latent_attention_kernel<T>, grid, dim3(kAttnHeads * 32), smem, (cudaStream_t)stream,
                q_abs, q_raw, q_raw_stride, q_raw_head, out, part, (const T*)c_pool, (const T*)r_pool, positions,
                request_of_token, table, table_width, num_pages, inv_freq, magnitude, interleaved, rot_dims, sink,
-               heads, rank, rot, page_size, scale, range_keys, ranges, err);
+               heads, rank, rot, page_size, scale, range_keys, ranges, window, err);
   })
   if (ranges > 1)
     CIE_LAUNCH("latent_merge", latent_merge_kernel, dim3(tokens, heads), dim3(128), 0, (cudaStream_t)stream, part, out,
-               positions, sink, heads, rank, range_keys, ranges);
+               positions, sink, heads, rank, range_keys, ranges, window);
   return 0;
 }

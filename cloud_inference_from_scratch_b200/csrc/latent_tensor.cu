@@ -104,7 +104,7 @@ latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __r
                                const int* __restrict__ table, int table_width, int num_pages,
                                const float* __restrict__ inv_freq, float magnitude, int interleaved, int rot_dims,
                                const float* __restrict__ sink, int tokens, int heads, int rank, int rot, int page_size,
-                               float scale, int range_keys, int ranges, int* err) {
+                               float scale, int range_keys, int ranges, int window, int* err) {
   extern __shared__ __align__(16) unsigned char shared_raw[];
   constexpr int CW = 8 * NT;
   constexpr int ROWS = kRows * RT;
@@ -146,7 +146,12 @@ latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __r
       position[RT - 1] = together ? positions[first_token + 1] : position[0];
     }
     const int length = position[RT - 1] + 1;
-    const int begin = blockIdx.z * range_keys;
+    // window > 0: a token sees its last `window` keys (itself included); the walk starts at the first key the
+    // earlier token of the tile sees, and the later token does not weigh that one
+    int lowest[RT];
+#pragma unroll
+    for (int tile = 0; tile < RT; ++tile) lowest[tile] = window > 0 ? max(0, position[tile] + 1 - window) : 0;
+    const int begin = lowest[0] + blockIdx.z * range_keys;
     if (begin >= length) continue;
     const int end = min(length, begin + range_keys);
     const int* pages = table + (size_t)request_of_token[token[0]] * table_width;
@@ -292,8 +297,8 @@ latent_attention_tensor_kernel(const float* __restrict__ q_abs, const float* __r
 #pragma unroll
       for (int tile = 0; tile < RT; ++tile) {
         const int last = min(end - 1, position[tile]);      // the later token of a pair sees one key more
-        in0[tile] = key0 <= last;
-        in1[tile] = key0 + 1 <= last;
+        in0[tile] = key0 <= last && key0 >= lowest[tile];
+        in1[tile] = key0 + 1 <= last && key0 + 1 >= lowest[tile];
         s[tile][0] = in0[tile] ? s[tile][0] * scale : -FLT_MAX;
         s[tile][1] = in1[tile] ? s[tile][1] * scale : -FLT_MAX;
         s[tile][2] = in0[tile] ? s[tile][2] * scale : -FLT_MAX;
@@ -435,7 +440,7 @@ extern "C" int cie_latent_attention_tensor(const float* q_abs, const float* q_ra
                                            int table_width, int num_pages, const float* inv_freq, float magnitude,
                                            int interleaved, int rot_dims, const float* sink, int tokens, int heads,
                                            int rank, int rot, int page_size, float scale, int range_keys, int ranges,
-                                           int pair_tokens, int* err, void* stream) {
+                                           int pair_tokens, int window, int* err, void* stream) {
   using namespace cie;
   if (tokens <= 0) return 0;
   if (!cie_latent_attention_tensor_supports(rank, rot)) CIE_FAIL("latent_attention_tensor: sizes %d + %d", rank, rot);
@@ -461,7 +466,8 @@ extern "C" int cie_latent_attention_tensor(const float* q_abs, const float* q_ra
     CIE_LAUNCH("latent_attention_tensor", (latent_attention_tensor_kernel<NT, RT>), grid, dim3(kWarps * 32), smem,  \
                (cudaStream_t)stream, q_abs, q_raw, q_raw_stride, q_raw_head, out, part, (const bf16*)c_pool,        \
                (const bf16*)r_pool, positions, request_of_token, table, table_width, num_pages, inv_freq, magnitude, \
-               interleaved, rot_dims, sink, tokens, heads, rank, rot, page_size, scale, range_keys, ranges, err);   \
+               interleaved, rot_dims, sink, tokens, heads, rank, rot, page_size, scale, range_keys, ranges, window, \
+               err);                                                                                                \
   }
 #define CIE_LATENT_TENSOR(NT)                        \
   if (row_tiles == 2) CIE_LATENT_TENSOR_RT(NT, 2)    \

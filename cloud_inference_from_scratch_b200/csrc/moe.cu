@@ -1,8 +1,10 @@
 // Routed experts (mixture of experts) for a flat batch of tokens:
 //
-//   route      router logits in float32 (token row times a float32 router matrix), a score function
-//              over all experts (softmax), the `top` largest of score + correction, and as mixing
-//              weights the scores of the chosen experts (optionally renormalised to sum 1)
+//   route      router logits in float32 (token row times a float32 router matrix, plus a bias if one is
+//              stored), a score function over all experts (softmax), the `top` largest of score +
+//              correction, and as mixing weights the scores of the chosen experts (optionally renormalised
+//              to sum 1); or (`chosen_softmax`) the `top` largest LOGITS and as weights the softmax over
+//              those logits alone
 //   plan       counts per expert -> offsets; every (token, choice) pair gets a place in its expert's
 //              run of rows; runs are cut into tiles of 128 rows for the grouped products
 //   gate_up    rows gathered by place, times the expert's stacked gate and up matrices, SiLU(gate)*up
@@ -34,7 +36,8 @@ __global__ void __launch_bounds__(kRouteWarps * 32)
 moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router,
                  const float* __restrict__ correction, int* __restrict__ ids,
                  float* __restrict__ weights, int* __restrict__ counts, int tokens,
-                 int hidden, int experts, int top, int renormalize) {
+                 int hidden, int experts, int top, int renormalize, const float* __restrict__ logit_bias,
+                 int chosen_softmax) {
   extern __shared__ __align__(16) float score_s[];      // [2 * experts]: scores, then choice scores; then the row
   pdl_wait();
   pdl_trigger();
@@ -72,11 +75,40 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router,
       for (int k = lane; k < hidden; k += 32) dot = fmaf(row_s[k], w[k], dot);
     }
     dot = warp_sum(dot);
-    if (lane == 0) score[e] = dot;
+    if (lane == 0) score[e] = logit_bias ? dot + logit_bias[e] : dot;
   }
   __syncthreads();
   if (warp != 0) return;
   __syncwarp();
+  if (chosen_softmax) {
+    // the largest logits win (lowest index on ties); their weights are exp(z - z_first) over the sum of those
+    for (int e = lane; e < experts; e += 32) choice[e] = score[e];
+    __syncwarp();
+    float first = 0.f, total = 0.f, mine = 0.f;
+    for (int j = 0; j < top; ++j) {
+      float best = -FLT_MAX;
+      int best_e = experts;
+      for (int e = lane; e < experts; e += 32)
+        if (choice[e] > best) { best = choice[e]; best_e = e; }
+      for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+        const int other_e = __shfl_xor_sync(0xffffffffu, best_e, offset);
+        if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+      }
+      if (j == 0) first = best;
+      const float w = expf(best - first);
+      total += w;
+      if (lane == j) mine = w;
+      if (lane == 0) {
+        ids[(size_t)t * top + j] = best_e;
+        choice[best_e] = -FLT_MAX;
+        atomicAdd(counts + best_e, 1);
+      }
+      __syncwarp();
+    }
+    if (lane < top) weights[(size_t)t * top + lane] = mine / total;
+    return;
+  }
   float m = -FLT_MAX;
   for (int e = lane; e < experts; e += 32) m = fmaxf(m, score[e]);
   m = warp_max(m);
@@ -419,7 +451,7 @@ extern "C" int cie_moe_row_tile() { return kRowTile; }
 extern "C" int cie_moe_route(const void* x, const float* router, const float* correction, int* ids,
                              float* weights, int* counts, int* offsets, int* cursors, int* place_to_pair,
                              int* tiles, int* tile_count, int tokens, int hidden, int experts, int top,
-                             int renormalize, int dtype, void* stream) {
+                             int renormalize, const float* logit_bias, int chosen_softmax, int dtype, void* stream) {
   if (tokens <= 0) return 0;
   if (experts < 1 || experts > kMaxExperts) CIE_FAIL("moe_route: 1..%d experts, got %d", kMaxExperts, experts);
   if (top < 1 || top > experts || top > 32) CIE_FAIL("moe_route: top %d of %d experts (at most 32)", top, experts);
@@ -433,13 +465,13 @@ extern "C" int cie_moe_route(const void* x, const float* router, const float* co
     if (smem > 48 * 1024 && cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       CIE_FAIL("moe_route: cannot reserve %zu bytes of shared memory", smem);
     CIE_LAUNCH("moe_route", moe_route_kernel<float>, dim3(blocks), dim3(warps * 32), smem, s, (const float*)x, router,
-               correction, ids, weights, counts, tokens, hidden, experts, top, renormalize);
+               correction, ids, weights, counts, tokens, hidden, experts, top, renormalize, logit_bias, chosen_softmax);
   } else if (dtype == kBFloat16) {
     if (smem > 48 * 1024 && cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       CIE_FAIL("moe_route: cannot reserve %zu bytes of shared memory", smem);
     CIE_LAUNCH("moe_route", moe_route_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, s,
                (const __nv_bfloat16*)x, router, correction, ids, weights, counts, tokens, hidden, experts, top,
-               renormalize);
+               renormalize, logit_bias, chosen_softmax);
   } else {
     CIE_FAIL("moe_route: unknown element type code %d", dtype);
   }

@@ -117,15 +117,20 @@ __global__ void __launch_bounds__(256) stream_norm_kernel(float* __restrict__ st
     dst[i] = from_float<T>((gain_single ? single : gain[i]) * (u_s[i] * inv));
 }
 
-// ---------------------------------------------------------------- q/k/v: norms and cache write
-// One block per token.  The source row is [q_heads*dim | kv_heads*dim | kv_heads*vdim] (+ bias).
-//   qk_norm  q and k are each divided by the root mean square of their WHOLE projection (all heads
-//            together) and multiplied by a gain vector of that size
+// ---------------------------------------------------------------- q/k/v: norms, rotation and cache write
+// One block per token.  The source row is [q_heads*dim | kv_heads*dim | kv_heads*vdim] (+ bias), of the
+// activation type or float32 (a product's float32 result that is not rounded before the norm).
+//   qk_norm  1: q and k are each divided by the root mean square of their WHOLE projection (all heads
+//            together) and multiplied by a gain vector of that size; 2: every head by its own root mean
+//            square, times a gain vector of a head's size that all heads share
 //   v_norm   every value head is divided by its own root mean square (no gain)
+//   rotation (inv_freq != nullptr) after the norms the first rot_dims elements of every q and k head turn by
+//            position * inv_freq[i], pair (i, i + rot_dims / 2) or, interleaved, (2i, 2i + 1); cos and sin
+//            are multiplied by `magnitude`; angle and rotation float32
 // q goes to q_out (row stride q_stride); k and v go to their page slots
 // ([page][kv_head][page_size][dim or vdim]).
-template <typename T>
-__global__ void norm_kv_write_kernel(const T* __restrict__ src, const float* __restrict__ bias,
+template <typename TI, typename T>
+__global__ void norm_kv_write_kernel(const TI* __restrict__ src, const float* __restrict__ bias,
                                      T* __restrict__ q_out, int q_stride,
                                      const int* __restrict__ positions,
                                      const int* __restrict__ request_of_token,
@@ -133,7 +138,9 @@ __global__ void norm_kv_write_kernel(const T* __restrict__ src, const float* __r
                                      T* __restrict__ k_pool, T* __restrict__ v_pool,
                                      const float* __restrict__ q_gain, const float* __restrict__ k_gain,
                                      int q_heads, int kv_heads, int dim, int vdim, int page_size,
-                                     int qk_norm, int v_norm, float eps, int write_cache, int src_stride, int* err) {
+                                     int qk_norm, int v_norm, float eps, int write_cache, int src_stride,
+                                     const float* __restrict__ inv_freq, int rot_dims, float magnitude,
+                                     int interleaved, int* err) {
   extern __shared__ float row_s[];
   __shared__ float scratch[33];
   pdl_wait();
@@ -141,7 +148,7 @@ __global__ void norm_kv_write_kernel(const T* __restrict__ src, const float* __r
   const int t = blockIdx.x;
   const int q_width = q_heads * dim, k_width = kv_heads * dim, v_width = kv_heads * vdim;
   const int width = q_width + k_width + v_width;
-  const T* row = src + (size_t)t * src_stride;
+  const TI* row = src + (size_t)t * src_stride;
   float sq_q = 0.f, sq_k = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float v = to_float(row[i]);
@@ -151,10 +158,12 @@ __global__ void norm_kv_write_kernel(const T* __restrict__ src, const float* __r
     else if (i < q_width + k_width) sq_k = fmaf(v, v, sq_k);
   }
   __syncthreads();
-  float inv_q = 1.f, inv_k = 1.f;
   if (qk_norm == 1) {
-    inv_q = rsqrtf(block_sum(sq_q, scratch) / (float)q_width + eps);
-    inv_k = rsqrtf(block_sum(sq_k, scratch) / (float)k_width + eps);
+    const float inv_q = rsqrtf(block_sum(sq_q, scratch) / (float)q_width + eps);
+    const float inv_k = rsqrtf(block_sum(sq_k, scratch) / (float)k_width + eps);
+    for (int i = threadIdx.x; i < q_width + k_width; i += blockDim.x)
+      row_s[i] = i < q_width ? q_gain[i] * (row_s[i] * inv_q) : k_gain[i - q_width] * (row_s[i] * inv_k);
+    __syncthreads();
   } else if (qk_norm == 2) {
     // every q and k head by its own root mean square, times a gain vector of the head's size that all heads
     // share; a warp takes a head at a time and leaves the finished head in the staged row
@@ -169,12 +178,27 @@ __global__ void norm_kv_write_kernel(const T* __restrict__ src, const float* __r
     }
     __syncthreads();
   }
-  const bool whole = qk_norm == 1;     // q and k are still to be scaled by the norm over their whole projection
-  T* q_row = q_out + (size_t)t * q_stride;
-  for (int i = threadIdx.x; i < q_width; i += blockDim.x)
-    q_row[i] = from_float<T>(whole ? q_gain[i] * (row_s[i] * inv_q) : row_s[i]);
-  if (!write_cache) return;
   const int pos = positions[t];
+  if (inv_freq) {
+    // a thread a pair: both elements are read before either is written, and no two pairs share an element
+    const int half = rot_dims / 2;
+    for (int e = threadIdx.x; e < (q_heads + kv_heads) * half; e += blockDim.x) {
+      const int h = e / half, i = e % half;
+      float* head = row_s + (size_t)h * dim;
+      const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
+      float sn, cs;
+      sincosf((float)pos * inv_freq[i], &sn, &cs);
+      sn *= magnitude;
+      cs *= magnitude;
+      const float u = head[a], v = head[b];
+      head[a] = u * cs - v * sn;
+      head[b] = v * cs + u * sn;
+    }
+    __syncthreads();
+  }
+  T* q_row = q_out + (size_t)t * q_stride;
+  for (int i = threadIdx.x; i < q_width; i += blockDim.x) q_row[i] = from_float<T>(row_s[i]);
+  if (!write_cache) return;
   const int request = request_of_token[t];
   const int index = pos / page_size;
   const int page = index < table_width ? table[(size_t)request * table_width + index] : -1;
@@ -186,8 +210,7 @@ __global__ void norm_kv_write_kernel(const T* __restrict__ src, const float* __r
   const float* k_row = row_s + q_width;
   for (int i = threadIdx.x; i < k_width; i += blockDim.x) {
     const int h = i / dim, d = i % dim;
-    const float v = whole ? k_gain[i] * (k_row[i] * inv_k) : k_row[i];
-    k_pool[(slot + (size_t)h * page_size) * dim + d] = from_float<T>(v);
+    k_pool[(slot + (size_t)h * page_size) * dim + d] = from_float<T>(k_row[i]);
   }
   // value heads: a warp per head at a time
   const float* v_row = k_row + k_width;
@@ -280,23 +303,34 @@ extern "C" int cie_norm_kv_write(const void* src, const float* bias, void* q_out
                                  int table_width, int num_pages, void* k_pool, void* v_pool,
                                  const float* q_gain, const float* k_gain, int tokens, int q_heads,
                                  int kv_heads, int dim, int vdim, int page_size, int qk_norm, int v_norm,
-                                 float eps, int write_cache, int src_stride, int dtype, int* err, void* stream) {
+                                 float eps, int write_cache, int src_stride, int src_dtype,
+                                 const float* inv_freq, int rot_dims, float magnitude, int interleaved,
+                                 int dtype, int* err, void* stream) {
   // qk_norm: 0 none; 1 over the whole projection (gains of the projection's size); 2 per head (gains of a
   // head's size, shared by the heads).  src_stride: elements from one source row to the next (0: the
-  // row holds q, k and v and nothing else).
+  // row holds q, k and v and nothing else).  src_dtype: float32 or the activation type `dtype`.
   if (tokens <= 0) return 0;
   if (qk_norm && (!q_gain || !k_gain)) CIE_FAIL("norm_kv_write: the q/k norm needs its gains");
   if (qk_norm < 0 || qk_norm > 2) CIE_FAIL("norm_kv_write: unknown q/k norm %d", qk_norm);
+  if (inv_freq && (rot_dims < 2 || rot_dims % 2 || rot_dims > dim))
+    CIE_FAIL("norm_kv_write: %d rotated elements of a head of %d", rot_dims, dim);
+  if (src_dtype != kFloat32 && src_dtype != dtype) CIE_FAIL("norm_kv_write: the source is float32 or of the activation type");
   const int width = q_heads * dim + kv_heads * (dim + vdim);
   if (src_stride == 0) src_stride = width;
   if (src_stride < width) CIE_FAIL("norm_kv_write: source rows of %d elements are shorter than q, k and v (%d)", src_stride, width);
   const size_t smem = (size_t)width * sizeof(float);
+#define CIE_NORM_KV(TI, T)                                                                                      \
+  do {                                                                                                           \
+    if (allow_shared(norm_kv_write_kernel<TI, T>, smem, "norm_kv_write")) return 1;                              \
+    CIE_LAUNCH("norm_kv_write", (norm_kv_write_kernel<TI, T>), dim3(tokens), dim3(256), smem, (cudaStream_t)stream, \
+               (const TI*)src, bias, (T*)q_out, q_stride, positions, request_of_token, table, table_width,       \
+               num_pages, (T*)k_pool, (T*)v_pool, q_gain, k_gain, q_heads, kv_heads, dim, vdim, page_size,       \
+               qk_norm, v_norm, eps, write_cache, src_stride, inv_freq, rot_dims, magnitude, interleaved, err);  \
+  } while (0)
   DISPATCH_DTYPE(dtype, "norm_kv_write", {
-    if (allow_shared(norm_kv_write_kernel<T>, smem, "norm_kv_write")) return 1;
-    CIE_LAUNCH("norm_kv_write", norm_kv_write_kernel<T>, dim3(tokens), dim3(256), smem, (cudaStream_t)stream,
-               (const T*)src, bias, (T*)q_out, q_stride, positions, request_of_token, table, table_width,
-               num_pages, (T*)k_pool, (T*)v_pool, q_gain, k_gain, q_heads, kv_heads, dim, vdim, page_size,
-               qk_norm, v_norm, eps, write_cache, src_stride, err);
+    if (src_dtype == kFloat32) CIE_NORM_KV(float, T);
+    else CIE_NORM_KV(T, T);
   })
+#undef CIE_NORM_KV
   return 0;
 }

@@ -11,8 +11,10 @@ model.py:221-225), multiply by the head and return float32 logits.
 Beyond the reference: a description may ask for a learned vector per position that is added to the
 embedding rows (``position_tensor``), for a sinusoid of the position instead (``position_wave_base``),
 for several copies of the residual stream side by side (``residual_streams``, [T, streams * H]; the
-blocks of such a model read and write the copies and the final norm reads their sum), and for a stored
-vector that is added to the stream right before a run of a layer (``ScheduleEntry.entry_offset``).
+blocks of such a model read and write the copies and the final norm reads their sum), for a stored
+vector that is added to the stream right before a run of a layer (``ScheduleEntry.entry_offset``), for the
+embedding rows to be added once more there (``ScheduleEntry.adds_embedding``), and for a constant on every
+sublayer's result (``residual_scale``).
 """
 
 from __future__ import annotations
@@ -201,6 +203,13 @@ class DecoderModel:
                              positions=ctx.positions, position_table=self.position_table, streams=streams)
         else:
             rt.ops.embedding(ctx.token_ids, self.embedding, residual, spec.embedding_scale)
+        embedded = None
+        if any(entry.adds_embedding for entry in spec.schedule):
+            # the stream as it is before the first layer, kept for the runs that add it again
+            if self.wave is not None or streams > 1 or self.position_table is not None:
+                raise ValueError("adding the embedding rows again is built for a plain embedding")
+            embedded = rt.workspace.get("embedded", ctx.num_tokens, spec.hidden_size, torch.float32)
+            rt.ops.embedding(ctx.token_ids, self.embedding, embedded, spec.embedding_scale)
         sink = rt.ops.residual_sink(residual) if self.norms_accept_accumulated and streams == 1 else None
         ctx.residual_sink = sink
         pending = None
@@ -212,9 +221,13 @@ class DecoderModel:
                 sink.following_gain = None
                 if index + 1 < len(spec.schedule):
                     sink.following_gain = self.layers[spec.schedule[index + 1].layer].block.entry_gain()
-            if entry.entry_offset is not None:
-                name, row = entry.entry_offset
-                rt.ops.add_rows(residual, pending, self.offsets[name][row])
+            if entry.entry_offset is not None or entry.adds_embedding:
+                vector = None
+                if entry.entry_offset is not None:
+                    name, row = entry.entry_offset
+                    vector = self.offsets[name][row]
+                rt.ops.add_rows(residual, pending, vector, base=embedded if entry.adds_embedding else None,
+                                scale=spec.residual_scale)
                 pending = None
             pending = self.layers[entry.layer].block.forward(
                 residual, pending, ctx, ctx.bindings[index]

@@ -3,7 +3,7 @@
 from __future__ import annotations
 
 GENERIC = ("elementwise.cu", "gemm_simt.cu", "gemm_stream.cu", "gemm_tcgen05.cu", "gemm_skinny.cu", "attention_generic.cu", "sampling.cu",
-           "streams.cu", "lightning.cu", "moe.cu", "moe_tcgen05.cu", "latent.cu", "latent_tensor.cu", "delta.cu", "recurrent.cu")
+           "streams.cu", "lightning.cu", "moe.cu", "moe_tcgen05.cu", "latent.cu", "latent_tensor.cu", "delta.cu", "recurrent.cu", "gla.cu")
 
 
 # head sizes the tensor-core attention library is built for ahead of time; any other multiple of

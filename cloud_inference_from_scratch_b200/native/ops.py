@@ -98,7 +98,9 @@ class Ops:
         self._silu_mul = ew.function("cie_silu_mul", [v, v, i, i, i, i, v])
         self._gated_act = ew.function("cie_gated_act", [v, i, v, v, i, i, f, f, f, i, v])
         self._embedding_wave = ew.function("cie_embedding_wave", [v, v, v, v, v, i, i, i, f, i, v, v])
-        self._add_rows = ew.function("cie_add_rows", [v, v, i, ll, v, i, i, v])
+        self._add_rows = ew.function("cie_add_rows", [v, v, i, ll, f, v, v, i, i, v])
+        self._add_layernorm = ew.function("cie_add_layernorm", [v, v, i, ll, f, v, v, v, v, i, i, f, i, v])
+        self._glu_act = ew.function("cie_glu_act", [v, i, v, i, i, i, i, v])
         self._unary_act = ew.function("cie_unary_act", [v, v, ll, i, i, v])
         self._sigmoid_gate = ew.function("cie_sigmoid_gate", [v, v, i, i, i, i, v])
         self._scaled_sum = ew.function("cie_scaled_sum", [v, v, f, f, ll, v])
@@ -117,6 +119,10 @@ class Ops:
             "cie_attention_generic_split",
             [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, i, f, i, v, v, i, v, v, i, i, v, v],
         )
+        self._attention_generic_sink = ag.function(
+            "cie_attention_generic_sink",
+            [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, i, f, i, v, v, i, v, v, i, v, i, v, v],
+        )
         self._group_share_floats = int(ag.handle.cie_attention_group_share_floats())
         self._group_tickets = None
         # libraries that only some models need are built and loaded when a part first asks for them
@@ -124,6 +130,7 @@ class Ops:
         self._lightning_lib = None
         self._latent_lib = None
         self._delta_lib = None
+        self._gla_lib = None
         self._recurrent_lib = None
         self._moe_lib = None
         self._sample = None   # sampling.cu is built when something is first sampled
@@ -213,7 +220,7 @@ class Ops:
 
     def attention_penalised(self, q: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
                             head_dim: int, value_dim: int, scale: float, window: int, distance: Any,
-                            keep_first: int = 0) -> None:
+                            keep_first: int = 0, sinks: Any = None) -> None:
         """Attention with the options of ``attention_generic`` (a value size of its own, a distance
         penalty, kept first keys), softmax weights float32 throughout.  bfloat16 prompt portions whose value heads have
         the size of the key heads run on the tensor cores (mma.sync; the weights enter the value
@@ -226,15 +233,15 @@ class Ops:
                 or os.environ.get("CIE_PENALISED_TC", "1") == "0"):
             self.attention_generic(q, out, ctx, kv, q_heads, kv_heads, head_dim, scale, window,
                                    value_dim=value_dim, distance=distance,
-                                   few_tokens=singles == ctx.num_requests, keep_first=keep_first)
+                                   few_tokens=singles == ctx.num_requests, keep_first=keep_first, sinks=sinks)
             return
         if singles:     # the leading rows of a mixed step are its single tokens
             self.attention_generic(q[:singles], out[:singles], ctx, kv, q_heads, kv_heads, head_dim, scale,
                                    window, value_dim=value_dim, distance=distance, few_tokens=True,
-                                   keep_first=keep_first)
+                                   keep_first=keep_first, sinks=sinks)
         plan = ctx.extras.get(("attention", q_heads // kv_heads)) or None
         fast.run_portions(q, out, ctx, kv, q_heads, kv_heads, scale, window, plan, distance, True,
-                          keep_first=keep_first)
+                          keep_first=keep_first, sinks=sinks)
 
     def require_attention(self, head_dim: int) -> None:
         """Builds, at model set-up, the attention kernels a head size needs."""
@@ -329,12 +336,37 @@ class Ops:
             self._add_rmsnorm(_ptr(residual), _ptr(update), 0, 0, None, _ptr(gain), _ptr(out),
                               _ptr(rows), count, hidden, eps, self._code_of(out), self.stream)
 
-    def add_rows(self, residual: Any, update: Any, vector: Any) -> None:
-        """residual[t] += vector (+ ``update``: None, an ``Accumulated`` (already added), or float32 terms as
-        ``Partials``), float32 in place: the stream as a run of layers that starts with a learned offset
-        finds it."""
+    def add_layernorm(self, residual: Any, update: Any, gain: Any, bias: Any, eps: float, out: Any,
+                      rows: Any = None, update_scale: float = 1.0) -> None:
+        """The layer norm with gain and bias of ``residual + update_scale * update`` (the sum stays in the float32
+        stream unless ``rows`` selects rows): ``update`` is None, a tensor [T, H] of the compute dtype or of
+        float32, or ``Partials`` without a pending bias."""
+        self._flush()
+        count, hidden = out.shape
+        self.launches += 1
+        if isinstance(update, Accumulated):
+            raise KernelError("add_layernorm: an update that is already in the stream cannot be scaled")
+        if isinstance(update, Partials) and (update.splits == 0 or update.bias is not None):
+            update = self.resolve(update, self.torch.empty(update.shape, dtype=self.torch.float32, device=self.device))
+        if (update is not None and not isinstance(update, Partials) and update.dtype == self.torch.float32
+                and self.code != F32):
+            update = Partials(update, 1, update.shape[0], update.shape[1], None)
+        if isinstance(update, Partials):
+            self._add_layernorm(_ptr(residual), _ptr(update.data), update.splits, update.stride, float(update_scale),
+                                _ptr(gain), _ptr(bias), _ptr(out), _ptr(rows), count, hidden, float(eps),
+                                self._code_of(out), self.stream)
+        else:
+            self._add_layernorm(_ptr(residual), _ptr(update), 0, 0, float(update_scale), _ptr(gain), _ptr(bias),
+                                _ptr(out), _ptr(rows), count, hidden, float(eps), self._code_of(out), self.stream)
+
+    def add_rows(self, residual: Any, update: Any, vector: Any, base: Any = None, scale: float = 1.0) -> None:
+        """residual[t] += vector + base[t] + scale * update, float32 in place: the stream as a run of layers that
+        starts with a learned offset finds it.  ``vector`` (float32 [H]) and ``base`` (float32 [T, H]) may be None;
+        ``update``: None, an ``Accumulated`` (already added; only with scale 1), or float32 terms as ``Partials``."""
         self._flush()
         if isinstance(update, Accumulated):
+            if scale != 1.0:
+                raise KernelError("add_rows: an update that is already in the stream cannot be scaled")
             update = None
         if update is not None and not isinstance(update, Partials):
             if update.dtype != self.torch.float32:
@@ -346,10 +378,21 @@ class Ops:
         tokens, hidden = residual.shape
         self.launches += 1
         if update is None:
-            self._add_rows(_ptr(residual), None, 0, 0, _ptr(vector), tokens, hidden, self.stream)
+            self._add_rows(_ptr(residual), None, 0, 0, 1.0, _ptr(base), _ptr(vector), tokens, hidden, self.stream)
         else:
-            self._add_rows(_ptr(residual), _ptr(update.data), update.splits, update.stride, _ptr(vector), tokens,
-                           hidden, self.stream)
+            self._add_rows(_ptr(residual), _ptr(update.data), update.splits, update.stride, float(scale), _ptr(base),
+                           _ptr(vector), tokens, hidden, self.stream)
+
+    def glu_act(self, gate_up: Any, out: Any, kind: str = "silu") -> None:
+        """out = act(gate) * up for contiguous ``gate_up`` [T, 2 * I] = [gate | up] (float32 or the compute dtype), in
+        float32, rounded once; ``kind``: "silu" or "gelu_tanh"."""
+        self._flush()
+        kinds = {"silu": 0, "gelu_tanh": 1}
+        if kind not in kinds:
+            raise KernelError(f"glu_act: unknown activation {kind!r} (known: {sorted(kinds)})")
+        self.launches += 1
+        self._glu_act(_ptr(gate_up), self._code_of(gate_up), _ptr(out), out.shape[0], out.shape[1], kinds[kind],
+                      self._code_of(out), self.stream)
 
     def unary_act(self, x: Any, out: Any, kind: str = "relu2") -> None:
         """out = act(x) for contiguous float32 ``x``, rounded once; "relu2": the square of relu."""
@@ -573,7 +616,8 @@ class Ops:
             self._embedding_streams = lib.function("cie_embedding_streams", [v, v, v, v, v, i, i, i, i, i, f, i, v, v])
             self._stream_norm = lib.function("cie_stream_norm", [v, i, v, i, v, v, v, v, i, v, v, i, i, f, i, v])
             self._norm_kv_write = lib.function(
-                "cie_norm_kv_write", [v, v, v, i, v, v, v, i, i, v, v, v, v, i, i, i, i, i, i, i, i, f, i, i, i, v, v])
+                "cie_norm_kv_write",
+                [v, v, v, i, v, v, v, i, i, v, v, v, v, i, i, i, i, i, i, i, i, f, i, i, i, v, i, f, i, i, v, v])
             self._streams_lib = lib
 
     def stream_norm(self, residual: Any, streams: int, update: Any, read: Any, gain: Any, eps: float,
@@ -604,14 +648,16 @@ class Ops:
 
     def norm_kv_write(self, qkv: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int, dim: int, vdim: int,
                       q_gain: Any, k_gain: Any, value_norm: bool, eps: float, q_buffer: Any,
-                      write_cache: bool = True, per_head: bool = False) -> Any:
+                      write_cache: bool = True, per_head: bool = False, rotation: Any = None) -> Any:
         """q and k of every token divided by the root mean square of their whole projection and
         multiplied by a gain vector (``q_gain`` None: left as they are), every value head divided by
         its own root mean square (``value_norm``); q goes to ``q_buffer``, k and v into the pages.
         ``per_head``: every q and k head is divided by its OWN root mean square instead, and the gains
         are vectors of a head's size that all heads share.
-        ``qkv`` is a tensor [T, (Hq + Hkv) * dim + Hkv * vdim] (its rows may go on with other columns,
-        which are left alone) or ``Partials`` with its bias pending."""
+        ``rotation`` (``inv_freq`` float32 [dims / 2], ``dims``, ``magnitude``, ``interleaved``): after the norms
+        the first ``dims`` elements of every q and k head turn by the token's position.
+        ``qkv`` is a tensor [T, (Hq + Hkv) * dim + Hkv * vdim] of the compute dtype or of float32 (its rows may
+        go on with other columns, which are left alone) or ``Partials`` with its bias pending."""
         self._flush()
         self._load_streams()
         bias = None
@@ -627,7 +673,11 @@ class Ops:
                             _ptr(kv.v), _ptr(q_gain), _ptr(k_gain), qkv.shape[0], q_heads, kv_heads, dim, vdim,
                             kv.page_size, 0 if q_gain is None else (2 if per_head else 1), 1 if value_norm else 0,
                             float(eps), 1 if write_cache else 0, qkv.stride(0), self._code_of(qkv),
-                            _ptr(self.error_word), self.stream)
+                            _ptr(rotation.inv_freq) if rotation is not None else None,
+                            int(rotation.dims) if rotation is not None else 0,
+                            float(rotation.magnitude) if rotation is not None else 1.0,
+                            int(rotation.interleaved) if rotation is not None else 0,
+                            self._code_of(q_buffer), _ptr(self.error_word), self.stream)
         return q_buffer
 
     # ------------------------------------------------------------------ linear attention with decay
@@ -707,6 +757,68 @@ class Ops:
         self._lightning_gate_norm(_ptr(o), o.stride(0), _ptr(gate), gate.stride(0), _ptr(gain), _ptr(out),
                                   out.shape[0], out.shape[1], float(eps), self._code_of(out), self.stream)
 
+    # ------------------------------------------------------------------ gated linear attention
+    def _load_gla(self) -> None:
+        if self._gla_lib is None:
+            v, i, f = c_void_p, c_int, c_float
+            lib = _Lib(load_library("gla.cu"))
+            self._gla_scan = lib.function(
+                "cie_gla_scan", [v, i, i, i, i, v, i, v, f, f, v, i, v, v, v, v, i, i, i, i, i, v, v])
+            self._gla_chunked = lib.function(
+                "cie_gla_chunked",
+                [v, i, i, i, i, v, i, v, f, f, v, i, v, v, v, v, v, v, v, v, i, i, i, i, i, i, v, v])
+            self.gla_scan_max_dim = int(lib.handle.cie_gla_scan_max_dim())
+            self.gla_chunk_tokens = int(lib.handle.cie_gla_chunk_tokens())
+            self.gla_chunk_max_dim = int(lib.handle.cie_gla_chunk_max_dim())
+            self._gla_lib = lib
+
+    def require_gla(self) -> int:
+        """Builds, at model set-up, the kernels of gated linear attention; returns the largest key size they take."""
+        self._load_gla()
+        return self.gla_scan_max_dim
+
+    def plan_gla(self, host: Any) -> dict[str, Any]:
+        """Chunk work lists of gated linear attention for a step that holds prompt portions (one list serves
+        every such layer); a step of single tokens runs the recurrence directly and needs none."""
+        if host.num_single == host.num_requests:
+            return {}
+        self._load_gla()
+        return self._plan_chunks(host, self.gla_chunk_tokens)
+
+    def gla(self, proj: Any, offsets: tuple[int, int, int], z: Any, z_bias: Any, tau: float, q_scale: float,
+            out: Any, state: Any, ctx: Any, heads: int, dim: int, vdim: int,
+            plan: dict[str, Any] | None = None) -> None:
+        """Gated linear attention over every request's new tokens from the state in its slot (``state``: float32
+        [slots, heads, dim, vdim]): ``S <- diag(alpha) S + k v^T``, ``o = S^T (q * q_scale)`` with
+        ``alpha = sigmoid(z + z_bias)^(1 / tau)`` per head and key channel.  ``proj`` is float32 [T, *] with q, k
+        and v at the columns ``offsets``; ``z`` float32 [T, heads * dim]; ``out`` float32 [T, heads * vdim].  With
+        ``plan`` (chunk lists of a step with prompt portions) and sizes the chunked kernels take, the recurrence
+        runs in chunks; else token by token."""
+        self._flush()
+        self._load_gla()
+        if proj.dtype != self.torch.float32 or z.dtype != self.torch.float32:
+            raise KernelError("gla: the projections enter the recurrence as float32 rows")
+        head = (_ptr(proj), proj.stride(0), int(offsets[0]), int(offsets[1]), int(offsets[2]), _ptr(z), z.stride(0),
+                _ptr(z_bias), 1.0 / float(tau), float(q_scale), _ptr(out), out.stride(0), _ptr(state))
+        chunked = (plan and dim <= self.gla_chunk_max_dim and vdim <= self.gla_chunk_max_dim
+                   and os.environ.get("CIE_GLA_CHUNKS", "1") != "0")
+        if chunked:
+            chunks = plan["chunk_row"].shape[0]
+            # room for the chunks of the largest step the runtime knows of (and a partial chunk for many requests),
+            # so that a long prompt after captured steps does not have to grow the buffers
+            most = max(chunks, self.max_rows // self.gla_chunk_tokens + 64)
+            sums = self.scratch(f"gla.chunks.{heads}x{dim}x{vdim}", chunks * heads * dim * vdim,
+                                reserve=most * heads * dim * vdim)
+            decays = self.scratch(f"gla.decays.{heads}x{dim}", chunks * heads * dim, reserve=most * heads * dim)
+            self.launches += 3
+            self._gla_chunked(*head, _ptr(sums), _ptr(decays), _ptr(plan["chunk_row"]), _ptr(plan["chunk_count"]),
+                              _ptr(plan["request_chunk_start"]), _ptr(ctx.slots), _ptr(ctx.request_active), chunks,
+                              ctx.num_requests, heads, dim, vdim, state.shape[0], _ptr(self.error_word), self.stream)
+            return
+        self.launches += 1
+        self._gla_scan(*head, _ptr(ctx.query_start), _ptr(ctx.slots), _ptr(ctx.request_active), ctx.num_requests,
+                       heads, dim, vdim, state.shape[0], _ptr(self.error_word), self.stream)
+
     # ------------------------------------------------------------------ attention over a cached latent
     def _load_latent(self) -> None:
         if self._latent_lib is None:
@@ -717,8 +829,8 @@ class Ops:
             self._head_linear = lib.function("cie_head_linear", [v, i, i, v, v, i, i, v, i, i, i, i, i, i, i, v])
             self._latent_attention = lib.function(
                 "cie_latent_attention",
-                [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, i, v, v])
-            self._latent_merge = lib.function("cie_latent_merge", [v, v, v, v, i, i, i, i, i, v])
+                [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, i, i, v, v])
+            self._latent_merge = lib.function("cie_latent_merge", [v, v, v, v, i, i, i, i, i, i, v])
             self._head_gather = lib.function("cie_head_gather", [v, i, i, v, i, i, i, v])
             self._head_scatter = lib.function("cie_head_scatter", [v, v, i, i, v, i, i, i, i, i, v])
             self.latent_max_rank = int(lib.handle.cie_latent_attention_max_rank())
@@ -728,7 +840,7 @@ class Ops:
                 tensor = _Lib(load_library("latent_tensor.cu"))
                 self._latent_tensor = tensor.function(
                     "cie_latent_attention_tensor",
-                    [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, i, v, v])
+                    [v, v, i, i, v, v, v, v, v, v, v, i, i, v, f, i, i, v, i, i, i, i, i, f, i, i, i, i, v, v])
                 self._latent_tensor_supports = tensor.handle.cie_latent_attention_tensor_supports
 
     def require_latent(self) -> int:
@@ -789,12 +901,13 @@ class Ops:
                           self._code_of(weight), self._code_of(out), self.stream)
 
     def latent_attention(self, q_latent: Any, q_raw: Any, q_raw_head: int, out: Any, ctx: Any, kv: Any, rotation: Any,
-                         sink: Any, heads: int, rank: int, rot: int, scale: float) -> None:
+                         sink: Any, heads: int, rank: int, rot: int, scale: float, window: int = 0) -> None:
         """Causal softmax attention of every (token, head) over the rows [latent | rotated key part] its
         request holds in the pages: ``q_latent`` float32 [T, heads, rank] meets the latents, the rotated
         part of ``q_raw`` (float32; head h starts at column ``h * q_raw_head``; rotated here) meets the key
         parts; ``out`` float32 [T, heads, rank] is the weighted sum of the latents.  ``sink`` (float32
-        [heads] or None) adds exp(sink_h) to the softmax denominator.  With few tokens the keys are cut
+        [heads] or None) adds exp(sink_h) to the softmax denominator.  ``window`` > 0: a token sees only its
+        last ``window`` keys, itself included.  With few tokens the keys are cut
         into ranges over CTAs and joined by a second kernel.  bfloat16 pages whose two parts are multiples
         of 8 elements run on the tensor cores (16 heads of a token a tile), everything else on the plain
         kernel (8 heads a CTA, a warp each)."""
@@ -808,6 +921,8 @@ class Ops:
         if tokens * groups < self.sm_count:
             # about two CTAs an SM: ranges of a multiple of 128 keys, counted over the longest context the tables hold
             longest = table.shape[1] * kv.page_size
+            if window > 0:
+                longest = min(longest, window)
             wanted = -(-2 * self.sm_count // (tokens * groups))
             range_keys = max(128, (-(-longest // wanted) + 127) // 128 * 128)
             ranges = max(1, -(-longest // range_keys))
@@ -825,18 +940,18 @@ class Ops:
                                 table.shape[1], kv.num_pages, _ptr(rotation.inv_freq), float(rotation.magnitude),
                                 int(rotation.interleaved), int(rotation.dims), _ptr(sink), tokens, heads, rank, rot,
                                 kv.page_size, float(scale), range_keys, ranges,
-                                0 if os.environ.get("CIE_LATENT_PAIRS", "1") == "0" else 1, _ptr(self.error_word),
-                                self.stream)
+                                0 if os.environ.get("CIE_LATENT_PAIRS", "1") == "0" else 1, int(window),
+                                _ptr(self.error_word), self.stream)
             if ranges > 1:
                 self._latent_merge(_ptr(scratch), _ptr(out), _ptr(ctx.positions), _ptr(sink), tokens, heads, rank,
-                                   range_keys, ranges, self.stream)
+                                   range_keys, ranges, int(window), self.stream)
             return
         self._latent_attention(_ptr(q_latent), _ptr(q_raw), q_raw.stride(0), q_raw_head, _ptr(out), _ptr(scratch),
                                _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions), _ptr(ctx.request_of_token), _ptr(table),
                                table.shape[1], kv.num_pages, _ptr(rotation.inv_freq), float(rotation.magnitude),
                                int(rotation.interleaved), int(rotation.dims), _ptr(sink), tokens, heads, rank, rot,
-                               kv.page_size, float(scale), range_keys, ranges, self.code, _ptr(self.error_word),
-                               self.stream)
+                               kv.page_size, float(scale), range_keys, ranges, int(window), self.code,
+                               _ptr(self.error_word), self.stream)
 
     # ------------------------------------------------------------------ generalized delta rule
     def _load_delta(self) -> None:
@@ -919,7 +1034,7 @@ class Ops:
         if self._moe_lib is None:
             v, i = c_void_p, c_int
             lib = _Lib(load_library("moe.cu"))
-            self._moe_route = lib.function("cie_moe_route", [v, v, v, v, v, v, v, v, v, v, v, i, i, i, i, i, i, v])
+            self._moe_route = lib.function("cie_moe_route", [v, v, v, v, v, v, v, v, v, v, v, i, i, i, i, i, v, i, i, v])
             self._moe_gate_up_simt = lib.function("cie_moe_gate_up_simt", [v, v, v, v, v, v, v, i, i, i, i, i, i, v])
             self._moe_down_simt = lib.function("cie_moe_down_simt", [v, v, v, v, v, v, i, i, i, i, i, i, v])
             self._moe_combine = lib.function("cie_moe_combine", [v, v, v, i, i, i, i, v])
@@ -952,11 +1067,13 @@ class Ops:
         return both.reshape(experts, 2 * ff, hidden).contiguous()
 
     def routed_experts(self, x: Any, router: Any, correction: Any, w_gate: Any, w_up: Any, w_down: Any,
-                       top: int, renormalize: bool, out: Any, workspace: Any) -> Any:
+                       top: int, renormalize: bool, out: Any, workspace: Any, router_bias: Any = None,
+                       chosen_softmax: bool = False) -> Any:
         """out[t] = sum over the ``top`` chosen experts e of score_e * down_e(SiLU(gate_e x) * up_e x).
         ``router`` float32 [E, H]; ``w_gate``/``w_up`` [E, F, H], or ``w_up`` None and ``w_gate`` the
         interleaved [E, 2F, H] of ``interleave_gate_up``; ``w_down`` [E, H, F]; ``out`` float32 or the
-        activation type."""
+        activation type.  ``router_bias`` (float32 [E]) is added to the router's logits; ``chosen_softmax``: the
+        experts with the largest logits are chosen and weighted by the softmax over their logits alone."""
         self._flush()
         self._load_moe()
         torch = self.torch
@@ -979,7 +1096,8 @@ class Ops:
         self.launches += 5
         self._moe_route(_ptr(x), _ptr(router), _ptr(correction), _ptr(ids), _ptr(weights), _ptr(counts),
                         _ptr(offsets), _ptr(cursors), _ptr(place_to_pair), _ptr(tiles), _ptr(tile_count), tokens,
-                        hidden, experts, top, 1 if renormalize else 0, code, self.stream)
+                        hidden, experts, top, 1 if renormalize else 0, _ptr(router_bias), 1 if chosen_softmax else 0,
+                        code, self.stream)
         aligned = (x.data_ptr() | w_gate.data_ptr() | w_down.data_ptr() | act.data_ptr()) % 16 == 0
         if w_up is None and not (code == BF16 and aligned):
             raise KernelError("routed_experts: interleaved gate/up weights are for aligned bfloat16 operands")
@@ -1356,17 +1474,19 @@ class Ops:
     def attention_generic(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int,
                           kv_heads: int, head_dim: int, scale: float, window: int,
                           value_dim: int | None = None, distance: Any = None, few_tokens: bool = False,
-                          keep_first: int = 0) -> None:
+                          keep_first: int = 0, sinks: Any = None) -> None:
         """``keep_first``: with a window, the request's first so many keys stay visible behind it.
         ``value_dim``: size of a value head when it is not ``head_dim``; ``distance``: (r1, r2),
         float32 [q_heads] each, of the penalty r1 * log(1 + r2 * (query position - key position)).
+        ``sinks``: float32 [q_heads]; exp(sinks[h]) joins the softmax denominator of head h.
         ``few_tokens``: the rows are single tokens of a decode step; their keys are then cut into
         ranges with a CTA each where the device would otherwise stand mostly idle."""
         self._flush()
         table = ctx.block_tables[kv.group]
         self.launches += 1
+        tokens = qkv.shape[0]
+        splits, shares, tickets = 1, None, None
         if few_tokens:
-            tokens = qkv.shape[0]
             units = tokens * kv_heads * -(-(q_heads // kv_heads) // 8)
             keys = table.shape[1] * kv.page_size
             if window > 0:
@@ -1374,39 +1494,18 @@ class Ops:
             # a range keeps at least 128 keys; no more CTAs than one an SM
             splits = max(1, min(keys // 128, self.sm_count // max(units, 1), 16))
             if splits > 1:
-                r1, r2 = distance if distance is not None else (None, None)
                 shares = self.scratch("attention.shares", units * splits * self._group_share_floats)
                 if self._group_tickets is None or self._group_tickets.numel() < units:
                     self._group_tickets = self.torch.zeros(max(units, 1024), dtype=self.torch.int32, device=self.device)
                     self.scratch_generation += 1
-                self._attention_generic_split(
-                    _ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions),
-                    _ptr(ctx.request_of_token), _ptr(table), table.shape[1], kv.num_pages, tokens, q_heads, kv_heads,
-                    head_dim, value_dim or head_dim, kv.page_size, scale, window, _ptr(r1), _ptr(r2), splits,
-                    _ptr(shares), _ptr(self._group_tickets), int(keep_first), self._code_of(qkv),
-                    _ptr(self.error_word), self.stream)
-                return
-        if keep_first:
-            r1, r2 = distance if distance is not None else (None, None)
-            self._attention_generic_split(
-                _ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions),
-                _ptr(ctx.request_of_token), _ptr(table), table.shape[1], kv.num_pages, qkv.shape[0], q_heads, kv_heads,
-                head_dim, value_dim or head_dim, kv.page_size, scale, window, _ptr(r1), _ptr(r2), 1, None, None,
-                int(keep_first), self._code_of(qkv), _ptr(self.error_word), self.stream)
-            return
-        if distance is not None or (value_dim or head_dim) != head_dim:
-            r1, r2 = distance if distance is not None else (None, None)
-            self._attention_generic_ex(_ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k),
-                                       _ptr(kv.v), _ptr(ctx.positions), _ptr(ctx.request_of_token),
-                                       _ptr(table), table.shape[1], kv.num_pages, qkv.shape[0], q_heads,
-                                       kv_heads, head_dim, value_dim or head_dim, kv.page_size, scale, window,
-                                       _ptr(r1), _ptr(r2), self._code_of(qkv), _ptr(self.error_word), self.stream)
-            return
-        self._attention_generic(_ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k),
-                                _ptr(kv.v), _ptr(ctx.positions), _ptr(ctx.request_of_token),
-                                _ptr(table), table.shape[1], kv.num_pages, qkv.shape[0], q_heads,
-                                kv_heads, head_dim, kv.page_size, scale, window,
-                                self._code_of(qkv), _ptr(self.error_word), self.stream)
+                tickets = self._group_tickets
+        r1, r2 = distance if distance is not None else (None, None)
+        self._attention_generic_sink(
+            _ptr(qkv), qkv.shape[1], _ptr(out), out.shape[1], _ptr(kv.k), _ptr(kv.v), _ptr(ctx.positions),
+            _ptr(ctx.request_of_token), _ptr(table), table.shape[1], kv.num_pages, tokens, q_heads, kv_heads,
+            head_dim, value_dim or head_dim, kv.page_size, scale, window, _ptr(r1), _ptr(r2), splits,
+            _ptr(shares), _ptr(tickets), int(keep_first), _ptr(sinks), self._code_of(qkv),
+            _ptr(self.error_word), self.stream)
 
     def silu_mul(self, gate_up: Any, out: Any, block: int | None = None) -> None:
         self._flush()

@@ -92,7 +92,7 @@ class TensorAttention:
         )
         self._prefill_ex = lib.function(
             "cie_attention_prefill_ex",
-            [v, i, v, i, v, v, v, i, i, v, v, i, v, v, v, i, i, i, i, f, i, v, v, i, i, v, v],
+            [v, i, v, i, v, v, v, i, i, v, v, i, v, v, v, i, i, i, i, f, i, v, v, i, i, v, v, v],
         )
         self._decode = lib.function(
             "cie_attention_decode",
@@ -330,11 +330,12 @@ class TensorAttention:
 
     def run_portions(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int, scale: float,
                      window: int, plan: dict[str, Any] | None, distance: Any, split_weights: bool,
-                     keep_first: int = 0) -> None:
+                     keep_first: int = 0, sinks: Any = None) -> None:
         """The prompt portions of a step (every request after the leading single tokens) on the
         mma.sync kernel, with the options the other kernels do not have: a distance penalty
         (``distance``: float32 vectors r1, r2 per query head), softmax weights that enter the value
-        product as two bfloat16 terms, and a request's first ``keep_first`` keys visible behind the window."""
+        product as two bfloat16 terms, a request's first ``keep_first`` keys visible behind the window, and a
+        sink term per query head in the softmax denominator (``sinks``: float32 [q_heads])."""
         ops = self.ops
         torch = ops.torch
         table = ctx.block_tables[kv.group]
@@ -351,7 +352,8 @@ class TensorAttention:
                          plan["tile_request"].shape[0], ctx.context_lens.data_ptr(), ctx.query_lens.data_ptr(),
                          ctx.query_start.data_ptr(), q_heads, kv_heads, kv.page_size, heads_per_tile(group),
                          scale, window, None if r1 is None else r1.data_ptr(), None if r2 is None else r2.data_ptr(),
-                         1 if split_weights else 0, int(keep_first), ops.error_word.data_ptr(), ops.stream)
+                         1 if split_weights else 0, int(keep_first), None if sinks is None else sinks.data_ptr(),
+                         ops.error_word.data_ptr(), ops.stream)
 
     def run(self, qkv: Any, out: Any, ctx: Any, kv: Any, q_heads: int, kv_heads: int,
             scale: float, window: int, plan: dict[str, Any] | None = None) -> bool:

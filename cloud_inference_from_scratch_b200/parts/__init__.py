@@ -1,5 +1,5 @@
 from . import (  # noqa: F401  (registers the built-in parts)
-    attention, block, connection, delta, gated_delta, latent, lightning, matrix_memory, mlp, norm, rotary, routed,
+    attention, block, connection, delta, gated_delta, gla, latent, lightning, matrix_memory, mlp, norm, rotary, routed,
     side_by_side,
 )
 from .base import (

@@ -29,11 +29,17 @@ Options beyond the reference, each a constant of the part so that any descriptio
   (the gate's weight is stacked under q, k and v: one product);
 * ``distance_penalty``: the score of query position i and key position j is lowered by
   ``r1_h * ln(1 + r2_h * (i - j))`` with two stored numbers per query head;
+* ``sink``: the softmax denominator of every query head holds one more term ``exp(sink_h)``, a stored number
+  per head that has no key and no value and is not scaled;
+* ``projection_float32``: q, k and v leave their product as float32 and are not rounded before the norms and
+  the rotation;
 * ``position=None``: no rotation;
 * ``names``: the tensor names, where a model stores them under others.
 
-With any of these but the last the layer runs product -> norms + cache write -> attention -> output
-projection with the kernels of those options; scores, softmax and norms are float32.
+With any of these but the last two the layer runs product -> norms + rotation + cache write -> attention ->
+output projection with the kernels of those options; scores, softmax, norms and angles are float32.  On that
+path the rotation (after the norms) takes either pairing, a part of the head, blended frequencies and a
+magnitude factor on cos and sin, all from the position part.
 """
 
 from __future__ import annotations
@@ -63,6 +69,8 @@ class Attention(Mixer):
         names: dict[str, str] | None = None,
         keep_first: int = 0,
         gate: bool = False,
+        sink: bool = False,
+        projection_float32: bool = False,
     ) -> None:
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
@@ -76,9 +84,9 @@ class Attention(Mixer):
         if keep_first < 0:
             raise ValueError("keep_first must not be negative")
         self.gate = bool(gate)
+        self.sink = bool(sink)
+        self.projection_float32 = bool(projection_float32)
         self.position = build_part("position", position) if position is not None else None
-        if getattr(self.position, "magnitude", 1.0) != 1.0 or getattr(self.position, "keep_pairing", False):
-            raise ValueError("this mixer's kernels rotate without a magnitude factor and pair (j, j + R/2) only")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.scale *= float(getattr(self.position, "attention_factor", 1.0))
         self.q_width = self.num_heads * self.head_dim
@@ -95,15 +103,16 @@ class Attention(Mixer):
         self.norm_eps = float(norm_eps)
         # the options that the rotary kernels and the tensor-core attention kernels do not know
         self.general = bool(self.qk_norm or self.value_norm or self.distance_penalty
-                            or self.value_dim != self.head_dim or self.keep_first or self.gate)
-        if self.general and self.position is not None:
-            raise ValueError("q/k norm, value norm, distance penalty, kept first keys, an output gate and a value "
-                             "size of its own are built for attention without rotation")
+                            or self.value_dim != self.head_dim or self.keep_first or self.gate or self.sink
+                            or self.projection_float32)
+        if not self.general and (getattr(self.position, "magnitude", 1.0) != 1.0
+                                 or getattr(self.position, "keep_pairing", False)):
+            raise ValueError("the fused rotary kernels rotate without a magnitude factor and pair (j, j + R/2) only")
         if self.gate and self.qkv_bias:
             raise ValueError("the output gate is built for projections without biases")
         self.names = {key: key for key in ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight",
                                            "q_proj.bias", "k_proj.bias", "v_proj.bias", "q_norm", "k_norm",
-                                           "r1", "r2", "gate")}
+                                           "r1", "r2", "gate", "sink")}
         self.names.update(names or {})
         self.tiled = False      # set at bind: whether prompt portions run on the tensor-core kernel
 
@@ -140,6 +149,8 @@ class Attention(Mixer):
             specs[n["k_norm"]] = TensorSpec((self.head_dim if per_head else self.kv_width,), init="gain", role="vector")
         if self.gate:
             specs[n["gate"]] = TensorSpec((self.out_width, self.hidden_size))
+        if self.sink:
+            specs[n["sink"]] = TensorSpec((self.num_heads,), role="vector")
         if self.distance_penalty:
             specs[n["r1"]] = TensorSpec((self.num_heads,), init="gain", role="vector")
             specs[n["r2"]] = TensorSpec((self.num_heads,), init="gain", role="vector")
@@ -154,12 +165,14 @@ class Attention(Mixer):
         # layout: a decode step then rotates and stores inside the projection's kernel, and the
         # separate rotary kernel (prompt portions) reads the same layout.
         rotary = self.position.rotary_dim if self.position is not None else 0
-        self.paired = bool(self.position is not None and getattr(ops, "can_pair_rotary", None)
+        self.paired = bool(self.position is not None and not self.general and getattr(ops, "can_pair_rotary", None)
                            and ops.can_pair_rotary(self.head_dim, rotary))
 
         # an encoding may want the elements of every q and k head stored in another order (its
-        # pairs side by side for the kernels); scores do not change when q and k move together
-        order = getattr(self.position, "row_order", lambda: None)()
+        # pairs side by side for the kernels); scores do not change when q and k move together.  The kernel
+        # of the general path rotates either pairing where the elements stand (gains of a q/k norm are stored
+        # by element and stay where they are)
+        order = None if self.general else getattr(self.position, "row_order", lambda: None)()
 
         def reorder(rows, heads):
             index = (torch.arange(heads).view(-1, 1) * self.head_dim + torch.tensor(order).view(1, -1)).reshape(-1)
@@ -179,8 +192,17 @@ class Attention(Mixer):
         self.w_qkv = ops.prepare_weight(stacked("weight"))
         self.b_qkv = stacked("bias") if self.qkv_bias else None
         self.w_o = runtime.ops.prepare_weight(tensors[self.names["o_proj.weight"]])
+        self.rotation = None
         if self.position is not None:
             self.position.bind({}, runtime)
+            if self.general:
+                from types import SimpleNamespace
+
+                inv_freq = torch.tensor(self.position.frequencies(), dtype=torch.float64).to(torch.float32)
+                self.rotation = SimpleNamespace(
+                    inv_freq=inv_freq.to(runtime.device).contiguous(), magnitude=self.position.magnitude,
+                    interleaved=self.position.pairing == "interleaved", dims=self.position.rotary_dim)
+        self.sinks = tensors[self.names["sink"]].contiguous() if self.sink else None
         self.q_gain = tensors[self.names["q_norm"]].contiguous() if self.qk_norm else None
         self.k_gain = tensors[self.names["k_norm"]].contiguous() if self.qk_norm else None
         self.distance = ((tensors[self.names["r1"]].contiguous(), tensors[self.names["r2"]].contiguous())
@@ -195,24 +217,32 @@ class Attention(Mixer):
     kernels_through_ops = True  # every kernel of this part is a method of ``Ops``: a decode step may be recorded
 
     def forward_general(self, x, ctx, binding):
-        """The layer with q/k norm, value norm, distance penalty or a value size of its own."""
+        """The layer with q/k norm, value norm, rotation after the norms, distance penalty, a sink or a value size of
+        its own."""
         import torch
 
         rt = self.runtime
         tokens = x.shape[0]
         kv = binding.kv
         width = self.qkv_width + (self.out_width if self.gate else 0)
-        qkv = rt.workspace.get("attention.qkv", tokens, width, rt.dtype)
-        qkv = rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv, tag="attention.qkv", defer_bias=True)
+        if self.projection_float32:
+            qkv = rt.workspace.get("attention.qkv32", tokens, width, torch.float32)
+            qkv = rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv)
+        else:
+            qkv = rt.workspace.get("attention.qkv", tokens, width, rt.dtype)
+            qkv = rt.ops.linear(x, self.w_qkv, self.b_qkv, qkv, tag="attention.qkv", defer_bias=True)
         q = rt.workspace.get("attention.q", tokens, self.q_width, rt.dtype)
         rt.ops.norm_kv_write(qkv, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim,
                              self.q_gain, self.k_gain, self.value_norm, self.norm_eps, q,
-                             write_cache=binding.owns_cache, per_head=self.qk_norm == "head")
+                             write_cache=binding.owns_cache, per_head=self.qk_norm == "head",
+                             rotation=self.rotation)
         mixed = rt.workspace.get("attention.out", tokens, self.out_width, rt.dtype)
         rt.ops.attention_penalised(q, mixed, ctx, kv, self.num_heads, self.num_kv_heads, self.head_dim,
                                    self.value_dim, self.scale, self.window, self.distance,
-                                   keep_first=self.keep_first)
+                                   keep_first=self.keep_first, sinks=self.sinks)
         if self.gate:
+            if self.projection_float32:
+                raise ValueError("the output gate reads a projection of the compute dtype")
             rt.ops.sigmoid_gate(mixed, qkv[:, self.qkv_width:])
         update = rt.workspace.get("mixer.update32", tokens, self.hidden_size, torch.float32)
         return rt.ops.linear(mixed, self.w_o, None, update)

@@ -19,8 +19,11 @@ product per head, with the gate in its epilogue).  Scores, weights, norms and an
 ``shares_cache``: the layer has no ``W_dkv`` and no latent norm of its own; it reads the rows another
 layer of equal ``kv_rank``, ``rot_dim`` and rotation wrote (the schedule's ``reads_cache_of``).
 
+``q_rank`` 0: no query latent; ``q = W_q h`` straight from the input (tensor ``q``).  ``window`` > 0: a query at
+position i sees the keys j with 0 <= i - j < window only, and the pages behind the window are given back.
+
 Tensor names (after the part's prefix): ``dq``, ``dq.norm``, ``uq``, ``dkv``, ``dkv.norm``, ``uk``, ``uv``,
-``sink``, ``g``, ``o``; ``names`` maps them to others.
+``sink``, ``g``, ``o``, and ``q`` when there is no query latent; ``names`` maps them to others.
 """
 
 from __future__ import annotations
@@ -30,14 +33,14 @@ from types import SimpleNamespace
 from ..config.spec import PartSpec
 from .base import CacheSpec, Mixer, TensorSpec, build_part, register_part
 
-NAMES = ("dq", "dq.norm", "uq", "dkv", "dkv.norm", "uk", "uv", "sink", "g", "o")
+NAMES = ("dq", "dq.norm", "uq", "dkv", "dkv.norm", "uk", "uv", "sink", "g", "o", "q")
 
 
 class LatentAttention(Mixer):
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, value_dim: int,
                  kv_rank: int, q_rank: int, scale: float, position: PartSpec, norm_eps: float,
                  sink: bool = False, gate: bool = False, shares_cache: bool = False,
-                 names: dict[str, str] | None = None) -> None:
+                 names: dict[str, str] | None = None, window: int = 0) -> None:
         self.hidden_size = int(hidden_size)
         self.num_heads = int(num_heads)
         self.head_dim = int(head_dim)
@@ -50,6 +53,9 @@ class LatentAttention(Mixer):
         self.sink = bool(sink)
         self.gate = bool(gate)
         self.shares_cache = bool(shares_cache)
+        self.window = int(window)
+        if self.window < 0 or self.q_rank < 0:
+            raise ValueError("latent attention: window and q_rank must not be negative")
         self.position = build_part("position", position)
         if self.position.rotary_dim > self.rot_dim:
             raise ValueError("the rotation covers more elements than the rotated part has")
@@ -60,19 +66,22 @@ class LatentAttention(Mixer):
 
     def cache_spec(self) -> CacheSpec:
         # one row of "keys" per token holds the latent, one row of "values" the rotated key part
-        return CacheSpec(kv_heads=1, head_dim=self.kv_rank, window=0,
+        return CacheSpec(kv_heads=1, head_dim=self.kv_rank, window=self.window,
                          value_dim=0 if self.rot_dim == self.kv_rank else self.rot_dim)
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         n, heads = self.names, self.num_heads
         specs = {
-            n["dq"]: TensorSpec((self.q_rank, self.hidden_size)),
-            n["dq.norm"]: TensorSpec((self.q_rank,), init="gain", role="vector"),
-            n["uq"]: TensorSpec((heads * self.q_head, self.q_rank)),
             n["uk"]: TensorSpec((heads * self.head_dim, self.kv_rank)),
             n["uv"]: TensorSpec((heads * self.value_dim, self.kv_rank)),
             n["o"]: TensorSpec((self.hidden_size, self.out_width)),
         }
+        if self.q_rank:
+            specs[n["dq"]] = TensorSpec((self.q_rank, self.hidden_size))
+            specs[n["dq.norm"]] = TensorSpec((self.q_rank,), init="gain", role="vector")
+            specs[n["uq"]] = TensorSpec((heads * self.q_head, self.q_rank))
+        else:
+            specs[n["q"]] = TensorSpec((heads * self.q_head, self.hidden_size))
         if not self.shares_cache:
             specs[n["dkv"]] = TensorSpec((self.kv_rank + self.rot_dim, self.hidden_size))
             specs[n["dkv.norm"]] = TensorSpec((self.kv_rank,), init="gain", role="vector")
@@ -90,22 +99,24 @@ class LatentAttention(Mixer):
         largest = ops.require_latent()
         if self.kv_rank > largest:
             raise ValueError(f"latent attention kernels take a latent of up to {largest}, got {self.kv_rank}")
-        # one product for everything that reads h: query latent, then latent and key part, then the gate
-        stacked = [tensors[n["dq"]]]
+        # one product for everything that reads h: query latent (or, without one, the queries themselves), then
+        # latent and key part, then the gate
+        stacked = [tensors[n["dq"] if self.q_rank else n["q"]]]
+        self.q_columns = stacked[0].shape[0]
         if not self.shares_cache:
             stacked.append(tensors[n["dkv"]])
         self.gate_column = sum(t.shape[0] for t in stacked)
         if self.gate:
             stacked.append(tensors[n["g"]])
         self.w_down = ops.prepare_weight(torch.cat(stacked))
-        self.w_uq = ops.prepare_weight(tensors[n["uq"]])
+        self.w_uq = ops.prepare_weight(tensors[n["uq"]]) if self.q_rank else None
         # per head [K, N]: the plain query part times W_uk[j] (dim -> kv_rank) is W_uk[j] as stored;
         # the latent sum times W_uv[j]^T (kv_rank -> vdim) is the stored [vdim, kv_rank] transposed
         self.w_absorb = ops.prepare_weight(tensors[n["uk"]]).view(heads, self.head_dim, self.kv_rank).contiguous()
         self.w_expand = (ops.prepare_weight(tensors[n["uv"]]).view(heads, self.value_dim, self.kv_rank)
                          .transpose(1, 2).contiguous())
         self.w_o = ops.prepare_weight(tensors[n["o"]])
-        self.q_gain = tensors[n["dq.norm"]].contiguous()
+        self.q_gain = tensors[n["dq.norm"]].contiguous() if self.q_rank else None
         self.kv_gain = tensors[n["dkv.norm"]].contiguous() if not self.shares_cache else None
         self.sinks = tensors[n["sink"]].contiguous() if self.sink else None
         self.position.bind({}, runtime)
@@ -125,16 +136,23 @@ class LatentAttention(Mixer):
         kv = binding.kv
         down = rt.workspace.get("latent.down", tokens, self.w_down.shape[0], f32)
         ops.linear(x, self.w_down, None, down)
-        q_latent = rt.workspace.get("latent.q_latent", tokens, self.q_rank, rt.dtype)
-        ops.latent_prepare(down, q_latent, self.q_gain, self.kv_gain, ctx, kv, self.rotation, self.q_rank,
-                           self.kv_rank, self.rot_dim, self.norm_eps, not self.shares_cache, binding.owns_cache)
-        q = rt.workspace.get("latent.q", tokens, heads * self.q_head, f32)
-        ops.linear(q_latent, self.w_uq, None, q)
+        if self.q_rank:
+            q_latent = rt.workspace.get("latent.q_latent", tokens, self.q_rank, rt.dtype)
+            ops.latent_prepare(down, q_latent, self.q_gain, self.kv_gain, ctx, kv, self.rotation, self.q_rank,
+                               self.kv_rank, self.rot_dim, self.norm_eps, not self.shares_cache, binding.owns_cache)
+            q = rt.workspace.get("latent.q", tokens, heads * self.q_head, f32)
+            ops.linear(q_latent, self.w_uq, None, q)
+        else:
+            # the queries are columns of the one product; what follows them is normalised, rotated and cached
+            q = down[:, :self.q_columns]
+            if not self.shares_cache:
+                ops.latent_prepare(down[:, self.q_columns:], None, None, self.kv_gain, ctx, kv, self.rotation, 0,
+                                   self.kv_rank, self.rot_dim, self.norm_eps, True, binding.owns_cache)
         q_absorbed = rt.workspace.get("latent.q_absorbed", tokens, heads * self.kv_rank, f32)
         ops.head_linear(q, self.q_head, self.w_absorb, q_absorbed, self.kv_rank, heads)
         summed = rt.workspace.get("latent.sum", tokens, heads * self.kv_rank, f32)
         ops.latent_attention(q_absorbed, q[:, self.head_dim:], self.q_head, summed, ctx, kv, self.rotation,
-                             self.sinks, heads, self.kv_rank, self.rot_dim, self.scale)
+                             self.sinks, heads, self.kv_rank, self.rot_dim, self.scale, window=self.window)
         mixed = rt.workspace.get("latent.out", tokens, self.out_width, rt.dtype)
         ops.head_linear(summed, self.kv_rank, self.w_expand, mixed, self.value_dim, heads,
                         gate=down[:, self.gate_column:] if self.gate else None)

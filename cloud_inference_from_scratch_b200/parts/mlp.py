@@ -128,3 +128,47 @@ class DenseActivation(FeedForward):
 
 
 register_part("feed_forward", "dense_activation", DenseActivation, replace=True)
+
+
+class GatedDense(FeedForward):
+    """Gated feed-forward with an activation by name: ``W_down (act(W_gate x) * (W_up x))``, no biases;
+    ``activation`` "gelu_tanh" (``0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))``) or "silu".  Gate and up are
+    one stacked product with float32 results; the activation and the multiply run in float32 in one kernel and
+    are rounded once; the result is float32 (a term of the residual sum).  Tensor names: ``gate``, ``up``,
+    ``down``."""
+
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh") -> None:
+        self.hidden_size = int(hidden_size)
+        self.intermediate_size = int(intermediate_size)
+        if activation not in ("gelu_tanh", "silu"):
+            raise ValueError(f"gated feed-forward: activation {activation!r} is not built (known: gelu_tanh, silu)")
+        self.activation = activation
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        inter, hidden = self.intermediate_size, self.hidden_size
+        return {"gate": TensorSpec((inter, hidden)), "up": TensorSpec((inter, hidden)),
+                "down": TensorSpec((hidden, inter))}
+
+    def bind(self, tensors, runtime) -> None:
+        import torch
+
+        self.runtime = runtime
+        self.w_gate_up = runtime.ops.prepare_weight(torch.cat([tensors["gate"], tensors["up"]]))
+        self.w_down = runtime.ops.prepare_weight(tensors["down"])
+
+    kernels_through_ops = True
+
+    def forward(self, x, ctx):
+        import torch
+
+        rt = self.runtime
+        tokens = x.shape[0]
+        both = rt.workspace.get("glu.gate_up", tokens, 2 * self.intermediate_size, torch.float32)
+        rt.ops.linear(x, self.w_gate_up, None, both)
+        hidden = rt.workspace.get("glu.hidden", tokens, self.intermediate_size, rt.dtype)
+        rt.ops.glu_act(both, hidden, self.activation)
+        update = rt.workspace.get("feed_forward.update32", tokens, self.hidden_size, torch.float32)
+        return rt.ops.linear(hidden, self.w_down, None, update)
+
+
+register_part("feed_forward", "gated_dense", GatedDense, replace=True)

@@ -61,6 +61,48 @@ class RMSNorm(Norm):
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
 
 
+class LayerNorm(Norm):
+    """Layer norm with gain and bias over the float32 stream, fused with the pending residual add:
+    ``gain * (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) + bias``, statistics in float32, one rounding.
+    ``update_scale``: the pending update is multiplied by this constant as it is added to the stream (a model
+    that scales every sublayer's result).  ``names``: the tensors' names after the part's prefix (``weight``,
+    ``bias``); ``bias=False``: no bias tensor."""
+
+    def __init__(self, hidden_size: int, eps: float, update_scale: float = 1.0, bias: bool = True,
+                 names: dict[str, str] | None = None) -> None:
+        self.hidden_size = int(hidden_size)
+        self.eps = float(eps)
+        self.update_scale = float(update_scale)
+        self.has_bias = bool(bias)
+        self.names = dict(weight="weight", bias="bias")
+        self.names.update(names or {})
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        specs = {self.names["weight"]: TensorSpec((self.hidden_size,), init="gain", role="vector")}
+        if self.has_bias:
+            specs[self.names["bias"]] = TensorSpec((self.hidden_size,), role="vector")
+        return specs
+
+    def bind(self, tensors, runtime) -> None:
+        self.runtime = runtime
+        self.weight = tensors[self.names["weight"]].contiguous()
+        self.bias = tensors[self.names["bias"]].contiguous() if self.has_bias else None
+
+    kernels_through_ops = True
+
+    def forward(self, residual, update, ctx, rows=None):
+        rt = self.runtime
+        count = residual.shape[0] if rows is None else rows.shape[0]
+        out = rt.workspace.get("norm.out" if rows is None else "norm.rows", count,
+                               self.hidden_size, rt.dtype, per_request=rows is not None)
+        rt.ops.add_layernorm(residual, update, self.weight, self.bias, self.eps, out, rows,
+                             update_scale=self.update_scale)
+        return out
+
+
+register_part("norm", "layernorm", LayerNorm, replace=True)
+
+
 class StreamRMSNorm(Norm):
     """RMS norm of what a sublayer reads from ``streams`` side-by-side copies of the residual
     stream (``residual``: float32 [T, streams * H]; one stream is the ordinary case):
