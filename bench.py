@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--impl own|reference]
-                    [--config 3b|7b-mixed|14b-pressure|zisesun|lodalix|lazilorn] [--quick]
+                    [--config 3b|7b-mixed|14b-pressure|zisesun|lodalix|lazilorn|bilipel] [--quick]
 
 Prints ONE JSON line.  The default configuration is the Qwen2.5-3B shape: a "step" is one decode
 step of a batch of requests whose prompts (2,048 random tokens each) were prefilled before;
@@ -36,6 +36,12 @@ of 256 and 512 tokens, and (unless ``--quick``) the two other benchmark configur
   and an output gate, beside a matrix memory; the gated delta rule with short convolutions; a squared-relu
   feed-forward; looped layers) at two sizes, beside the Qwen2 dense shape of equal width, layer runs, head
   count and feed-forward size and beside the Zisesun configuration of that size, measured the same way.
+
+* ``bilipel``: the Bilipel design (softmax attention with a norm over the whole q and k projections, partly
+  rotated heads and a sink; windowed latent attention with a sink; gated linear attention with a decay per key
+  channel; a gated dense feed-forward or routed experts; layer norms; looped layers) at two sizes, beside the
+  Qwen2 dense shape of equal width, layer runs, head count and active feed-forward size and beside the Lodalix
+  configuration of that size, measured the same way.
 
 ``check`` compares, at the full 36 layers, the logits of the bfloat16 generation path with the
 32-bit path of the same weights (``engine/check.py``).  ``--config`` prints the line of one of the
@@ -644,6 +650,40 @@ LAZILORN_SIZES = {
 }
 
 
+def _bilipel(width, layers, loop, heads, kv_heads, dim, rot_dim, kv_rank, window, gla_heads, ff, experts, top,
+             expert_ff, vocab=32000) -> dict:
+    """``layers``: a string of A (softmax attention with a sink, with a dense feed-forward), L (windowed latent
+    attention, routed experts) and G (gated linear attention, routed experts); ``loop``: (start, stop, times)."""
+    rot = dict(base=250000.0, dims=dim // 2, scaling=dict(factor=8.0, original=1024, fast=32.0, slow=1.0))
+    moe = dict(kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, top=top))
+    kinds = {
+        "A": dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, rot=rot),
+                  mlp=dict(kind="dense", ff=ff)),
+        "L": dict(type="latent_attention",
+                  mixer=dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=dim, kv_rank=kv_rank, scale=(dim + rot_dim) ** -0.5,
+                             rot=dict(base=10000.0, dims=rot_dim), mask=dict(size=window)), mlp=moe),
+        "G": dict(type="gla", mixer=dict(heads=gla_heads, dim=dim, vdim=dim, tau=16.0, decay_rank=64), mlp=moe),
+    }
+    raw = dict(architecture="Bilipel", vocab=vocab, width=width, norm=dict(eps=1e-5), residual_mult=0.3,
+               layers=[kinds[letter] for letter in layers])
+    if loop is not None:
+        raw["loop"] = dict(start=loop[0], stop=loop[1], times=loop[2])
+    return raw
+
+
+# (Bilipel configuration, the Qwen2 dense shape of equal width, layer runs, heads and ACTIVE feed-forward size, and
+# the Lodalix configuration of that size: the design whose mixers are nearest, latent attention with a sink and a
+# float32 matrix recurrence that decays per key channel).  w2048: six layers of which two run twice (eight layer
+# runs: A LG LG A L G); w4096: three layers of which the last runs twice (A L G G).
+BILIPEL_SIZES = {
+    "w2048": (_bilipel(2048, "ALGALG", (1, 3, 2), 16, 2, 128, 64, 512, 1024, 16, 5504, 16, 4, 1376),
+              dict(_qwen2(2048, 8, 16, 2, 5504, 32000, False)), LODALIX_SIZES["w2048"][0]),
+    "w4096": (_bilipel(4096, "ALG", (2, 3, 2), 32, 8, 128, 64, 512, 1024, 32, 8192, 32, 4, 2048),
+              dict(_qwen2(4096, 4, 32, 8, 8192, 32000, False)), LODALIX_SIZES["w4096"][0]),
+}
+NEAREST_DESIGN = {"lazilorn": "zisesun", "bilipel": "lodalix"}
+
+
 def _time_step_function(cfg: dict, batch: int, steps: int, warmup: int, only: str = "all") -> dict:
     """Prefill of one PROMPT_TOKENS prompt in one step (median of 5 after 3), then ``steps`` decode
     steps of ``batch`` requests that each hold a PROMPT_TOKENS context, through the step function;
@@ -715,7 +755,9 @@ def run_design(args: argparse.Namespace, design: str = "zisesun") -> int:
     """A second or third design at its sizes beside the Qwen2 dense shape of equal size."""
     import torch
 
-    sizes = {"zisesun": ZISESUN_SIZES, "lodalix": LODALIX_SIZES, "lazilorn": LAZILORN_SIZES}[design]
+    sizes = {"zisesun": ZISESUN_SIZES, "lodalix": LODALIX_SIZES, "lazilorn": LAZILORN_SIZES,
+             "bilipel": BILIPEL_SIZES}[design]
+    near = NEAREST_DESIGN.get(design)
     title = design.capitalize()
 
     if not torch.cuda.is_available():
@@ -727,8 +769,8 @@ def run_design(args: argparse.Namespace, design: str = "zisesun") -> int:
     for name, (zisesun, qwen, *nearest) in sizes.items():
         if args.size not in ("all", name):
             continue
-        if args.layers and design == "lazilorn":
-            print("bench.py: --layers does not go with --config lazilorn (its layer runs come from a loop)")
+        if args.layers and design in ("lazilorn", "bilipel"):
+            print(f"bench.py: --layers does not go with --config {design} (its layer runs come from a loop)")
             return 2
         if args.layers:
             zisesun = dict(zisesun, layers=zisesun["layers"][:args.layers])
@@ -738,11 +780,11 @@ def run_design(args: argparse.Namespace, design: str = "zisesun") -> int:
             points[name][design] = _time_step_function(zisesun, args.batch, args.steps, args.warmup, args.only)
         if args.model in ("both", "qwen2"):
             points[name]["qwen2_dense"] = _time_step_function(qwen, args.batch, args.steps, args.warmup, args.only)
-        if nearest and args.model in ("both", "zisesun"):
-            points[name]["zisesun"] = _time_step_function(nearest[0], args.batch, args.steps, args.warmup, args.only)
+        if nearest and args.model in ("both", near):
+            points[name][near] = _time_step_function(nearest[0], args.batch, args.steps, args.warmup, args.only)
         points[name]["layers"] = len(zisesun["layers"])
     first = next(iter(points.values()))
-    main = first.get(design) or first.get("qwen2_dense") or first["zisesun"]
+    main = first.get(design) or first.get("qwen2_dense") or first[near]
     line = {"metric": f"decode tok/s, {title} design at width 2,048 (8 requests at context 2,048), step function",
             "value": main["decode_tokens_per_s"], "unit": "tokens/s", "higher_is_better": True,
             "ms_per_step": main["decode_ms_per_step"], "steps": args.steps, "n_gpus": 1, "warmup": args.warmup,
@@ -789,10 +831,12 @@ def main() -> int:
                              "default is 2048; longer ones are for profiles of long contexts, own arm only)")
     parser.add_argument("--impl", default="own", choices=("own", "reference"))
     parser.add_argument("--size", default="all", help="--config zisesun or lodalix: one of its sizes (w2048, w4096)")
-    parser.add_argument("--model", default="both", choices=("both", "zisesun", "lodalix", "lazilorn", "qwen2"),
-                        help="--config zisesun, lodalix or lazilorn: only that design, or only its dense peer "
-                             "(--config lazilorn --model zisesun: only the Zisesun configuration of that size)")
-    parser.add_argument("--config", default="3b", choices=("3b", "7b-mixed", "14b-pressure", "zisesun", "lodalix", "lazilorn"),
+    parser.add_argument("--model", default="both", choices=("both", "zisesun", "lodalix", "lazilorn", "bilipel", "qwen2"),
+                        help="--config zisesun, lodalix, lazilorn or bilipel: only that design, or only its dense peer "
+                             "(--config lazilorn --model zisesun, --config bilipel --model lodalix: only the nearest "
+                             "design's configuration of that size)")
+    parser.add_argument("--config", default="3b",
+                        choices=("3b", "7b-mixed", "14b-pressure", "zisesun", "lodalix", "lazilorn", "bilipel"),
                         help="the benchmark configuration whose line is printed (default: the 3B line, "
                              "which also carries the other two as points)")
     parser.add_argument("--quick", action="store_true",
@@ -816,7 +860,7 @@ def main() -> int:
         CONTEXT = min(limit, PROMPT_TOKENS + max(2048, room))
     if args.impl == "reference":
         return run_reference(args)
-    if args.config in ("zisesun", "lodalix", "lazilorn"):
+    if args.config in ("zisesun", "lodalix", "lazilorn", "bilipel"):
         return run_design(args, args.config)
     if args.config != "3b":
         return run_other_config(args)

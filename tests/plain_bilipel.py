@@ -117,7 +117,7 @@ def latent_mixer(h, w, m, eps):
     k_turned = rotate(down[:, rank:].view(tokens, 1, rot_dim), positions, rot, True)[:, 0]
     k_plain = (latent @ w["uk"].T).view(tokens, heads, dim)
     values = (latent @ w["uv"].T).view(tokens, heads, vdim)
-    seen = visibility(tokens, m["mask"]["size"])
+    seen = visibility(tokens, (m.get("mask") or {}).get("size", 0))
     out = []
     for head in range(heads):
         scores = (q_plain[:, head] @ k_plain[:, head].T + q_turned[:, head] @ k_turned.T) * m["scale"]
@@ -172,13 +172,18 @@ def sub(weights, prefix):
     return {name[len(prefix):]: tensor.to(F64) for name, tensor in weights.items() if name.startswith(prefix)}
 
 
-def run_layer(x, config, weights, index):
-    layer, eps, mult = config["layers"][index], config["norm"]["eps"], config["residual_mult"]
+def rounded(h, on):
+    """The sublayer's input as a bfloat16 product would see it (``on``), or as it is."""
+    return h.to(torch.bfloat16).to(F64) if on else h
+
+
+def run_layer(x, config, weights, index, round_inputs=False):
+    layer, eps, mult = config["layers"][index], config["norm"]["eps"], config.get("residual_mult", 1.0)
     w = sub(weights, f"l{index}.")
-    x = x + mult * MIXERS[layer["type"]](layer_norm(x, w["norm1"], w["norm1.b"], eps), sub(w, "mix."),
-                                         layer["mixer"], eps)
+    h = rounded(layer_norm(x, w["norm1"], w["norm1.b"], eps), round_inputs)
+    x = x + mult * MIXERS[layer["type"]](h, sub(w, "mix."), layer["mixer"], eps)
     if layer.get("mlp"):
-        h = layer_norm(x, w["norm2"], w["norm2.b"], eps)
+        h = rounded(layer_norm(x, w["norm2"], w["norm2.b"], eps), round_inputs)
         ff = sub(w, "mlp.")
         x = x + mult * (dense_feed_forward(h, ff) if layer["mlp"]["kind"] == "dense"
                         else routed_feed_forward(h, ff, layer["mlp"]))
@@ -196,8 +201,29 @@ def run_order(config):
     return order + [(i, None) for i in range(loop["stop"], count)]
 
 
-def forward(config, weights, tokens, streams=None):
-    """Logits [T, vocab] of one sequence in float64.  ``streams``: a list that receives the stream after every layer run."""
+def read_folder(folder):
+    """config.json as a dictionary and the stored tensors by name."""
+    import json
+    from pathlib import Path
+
+    import safetensors.torch
+
+    with open(Path(folder) / "config.json", encoding="utf-8") as handle:
+        config = json.load(handle)
+    return config, safetensors.torch.load_file(str(Path(folder) / "model.safetensors"))
+
+
+def greedy(config, weights, prompt, count):
+    """``count`` tokens after ``prompt``, each the argmax (lowest index on ties) of the whole sequence so far."""
+    tokens = list(prompt)
+    for _ in range(count):
+        tokens.append(int(torch.argmax(forward(config, weights, tokens)[-1])))
+    return tokens[len(prompt):]
+
+
+def forward(config, weights, tokens, streams=None, round_inputs=False):
+    """Logits [T, vocab] of one sequence in float64.  ``streams``: a list that receives the stream after every layer
+    run.  ``round_inputs``: every sublayer reads its input rounded to bfloat16 (everything else stays exact)."""
     w = {name: tensor.to(F64) for name, tensor in weights.items()}
     embedded = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     x = embedded
@@ -206,7 +232,7 @@ def forward(config, weights, tokens, streams=None):
             if number > 0:
                 x = x + embedded
             x = x + w["loop.step"][number]
-        x = run_layer(x, config, weights, index)
+        x = run_layer(x, config, weights, index, round_inputs)
         if streams is not None:
             streams.append(x)
     x = layer_norm(x, w["final.norm"], w["final.norm.b"], config["norm"]["eps"])
