@@ -203,14 +203,14 @@ def drawn_configuration(seed):
             dim = rng.choice([8, 16, 24, 32, 48, 64, 96, 128])
             vdim = dim if rng.random() < 0.5 else rng.choice([8, 16, 40, 64, 128, 160])
             layer = attention(kv * group, kv, dim, vdim, rng.choice([2, dim // 2, dim]) // 2 * 2,
-                              rng.choice([0.4, 1.2, 4.0]) / dim ** 0.5, rng.choice([100.0, 10000.0, 250000.0]),
+                              rng.choice([0.4, 1.2, 3.0]) / dim ** 0.5, rng.choice([100.0, 10000.0, 250000.0]),
                               rng.random() < 0.5)
         elif kind == "latent":
-            rot_dim = rng.choice([2, 8, 16, 32, 64])
-            layer = latent(rng.choice([1, 2, 5, 8, 16, 20]), rng.choice([4, 16, 32, 64, 128]), rot_dim,
+            rot_dim, dim = rng.choice([2, 8, 16, 32, 64]), rng.choice([4, 16, 32, 64, 128])
+            layer = latent(rng.choice([1, 2, 5, 8, 16, 20]), dim, rot_dim,
                            rng.choice([8, 32, 64, 100]), rng.choice([8, 24, 64, 96, 256, 520]),
-                           rng.choice([0, 1, 2, 5, 16, 17, 33, 64, 100, 500]), rng.choice([0.05, 0.15, 0.4]),
-                           rng.choice([100.0, 10000.0]))
+                           rng.choice([0, 1, 2, 5, 16, 17, 33, 64, 100, 500]),
+                           rng.choice([0.4, 1.2, 3.0]) / (dim + rot_dim) ** 0.5, rng.choice([100.0, 10000.0]))
         else:
             layer = gla(rng.choice([1, 2, 3, 8]), rng.choice([4, 16, 32, 64, 128, 160]), rng.choice([8, 32, 64, 128, 136]),
                         rng.choice([1.0, 4.0, 16.0]), rng.choice([1, 4, 16, 24]))
@@ -345,7 +345,8 @@ def test_gated_activations(dtype):
     for kind, act in (("gelu_tanh", plain.gelu_tanh), ("silu", plain.silu)):
         out = torch.empty(7, 37, dtype=rt.dtype).cuda()
         rt.ops.glu_act(both.cuda(), out, kind)
-        close(out, act(both[:, :37].double()) * both[:, 37:].double(), dtype, scale=1.0, loose=5e-2, tight=2e-6)
+        want = act(both[:, :37].double()) * both[:, 37:].double()
+        close(out, want, dtype, scale=float(want.abs().max()), loose=5e-3, tight=1e-6)
 
 
 def fake_step(lengths, contexts, page, dtype, heads, dim, vdim, seed=0):
@@ -449,7 +450,8 @@ def test_attention_norm_rotation_sink_and_one_far_key_that_stands_out(dtype, dim
             rt.ops.attention_penalised(q_all[held:].contiguous(), out, step, kv, heads, groups, dim, vdim, scale, 0, None,
                                        sinks=sink.cuda())
             rt.ops.check_errors()
-            close(out.view(n - held, heads, vdim), want[held:], dtype, scale=1.0, loose=6e-2, tight=3e-5)
+            # the key that stands out scores up to 40: float32 rounding of that score moves its weight by 1e-5
+            close(out.view(n - held, heads, vdim), want[held:], dtype, scale=1.0, loose=6e-2, tight=1e-4)
         close(q_all.view(n, heads, dim), q, dtype, scale=1.0, loose=4e-2, tight=3e-5)
 
 
