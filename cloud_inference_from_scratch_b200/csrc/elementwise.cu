@@ -255,6 +255,85 @@ __global__ void add_layernorm_kernel(float* __restrict__ residual, const void* _
   }
 }
 
+// The same with 16-byte accesses, for rows whose length is a multiple of 4 (up to 16 * blockDim elements) and an
+// update of float32 terms or none: a thread owns up to kLayerPieces pieces of four neighbouring elements,
+// blockDim pieces apart, keeps them in registers across both reductions and writes stream and result back
+// the same way.
+constexpr int kLayerPieces = 4;
+
+template <typename T>
+__device__ __forceinline__ void store4(T* dst, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float a, float b, float c, float d) {
+  uint2 packed;
+  *reinterpret_cast<__nv_bfloat162*>(&packed.x) = __floats2bfloat162_rn(a, b);
+  *reinterpret_cast<__nv_bfloat162*>(&packed.y) = __floats2bfloat162_rn(c, d);
+  *reinterpret_cast<uint2*>(dst) = packed;
+}
+
+template <typename T>
+__global__ void add_layernorm_x4_kernel(float* __restrict__ residual, const float* __restrict__ update,
+                                        int partial_splits, size_t partial_stride, float update_scale,
+                                        const float* __restrict__ gain, const float* __restrict__ bias,
+                                        T* __restrict__ out, const int* __restrict__ rows, int hidden, float eps) {
+  __shared__ float scratch[33];
+  pdl_trigger();   // see add_rmsnorm_kernel
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * hidden;
+  const float* part = update ? update + (size_t)src * hidden : nullptr;
+  const bool write_back = rows == nullptr && update != nullptr;
+  const int pieces = hidden / 4;
+  float4 x[kLayerPieces];
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < kLayerPieces; ++j) {
+    const int piece = threadIdx.x + j * blockDim.x;
+    x[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (piece < pieces) {
+      x[j] = *reinterpret_cast<const float4*>(res + 4 * piece);
+      if (part) {
+        float4 u = *reinterpret_cast<const float4*>(part + 4 * piece);
+        for (int s = 1; s < partial_splits; ++s) {
+          const float4 more = *reinterpret_cast<const float4*>(part + (size_t)s * partial_stride + 4 * piece);
+          u.x += more.x; u.y += more.y; u.z += more.z; u.w += more.w;
+        }
+        x[j].x = fmaf(update_scale, u.x, x[j].x);
+        x[j].y = fmaf(update_scale, u.y, x[j].y);
+        x[j].z = fmaf(update_scale, u.z, x[j].z);
+        x[j].w = fmaf(update_scale, u.w, x[j].w);
+      }
+      sum += (x[j].x + x[j].y) + (x[j].z + x[j].w);
+    }
+  }
+  const float mean = block_sum(sum, scratch) / (float)hidden;
+  float sq = 0.f;
+#pragma unroll
+  for (int j = 0; j < kLayerPieces; ++j) {
+    if (threadIdx.x + j * blockDim.x < pieces) {
+      const float a = x[j].x - mean, b = x[j].y - mean, c = x[j].z - mean, d = x[j].w - mean;
+      sq = fmaf(a, a, sq); sq = fmaf(b, b, sq); sq = fmaf(c, c, sq); sq = fmaf(d, d, sq);
+    }
+  }
+  const float inv = rsqrtf(block_sum(sq, scratch) / (float)hidden + eps);
+  T* dst = out + (size_t)r * hidden;
+#pragma unroll
+  for (int j = 0; j < kLayerPieces; ++j) {
+    const int piece = threadIdx.x + j * blockDim.x;
+    if (piece >= pieces) continue;
+    if (write_back) *reinterpret_cast<float4*>(res + 4 * piece) = x[j];
+    const float4 g = *reinterpret_cast<const float4*>(gain + 4 * piece);
+    const float4 b = bias ? *reinterpret_cast<const float4*>(bias + 4 * piece) : make_float4(0.f, 0.f, 0.f, 0.f);
+    store4<T>(dst + 4 * piece, fmaf(g.x, (x[j].x - mean) * inv, b.x), fmaf(g.y, (x[j].y - mean) * inv, b.y),
+              fmaf(g.z, (x[j].z - mean) * inv, b.z), fmaf(g.w, (x[j].w - mean) * inv, b.w));
+  }
+}
+
 // ---------------------------------------------------------------- rotary + paged KV write
 // qkv: [T, (Hq + 2 Hkv) * D], q heads first, then k heads, then v heads.  q is rotated in place.
 // k is rotated and written, v is copied, to pool[page][kv_head][pos % page][D] with
@@ -808,6 +887,22 @@ extern "C" int cie_add_layernorm(float* residual, const void* update, int partia
                                  float eps, int dtype, void* stream) {
   if (count <= 0) return 0;
   if (partial_splits > kMaxSplits) CIE_FAIL("add_layernorm: at most %d float32 terms, got %d", kMaxSplits, partial_splits);
+  const bool float_terms = update == nullptr || partial_splits > 0 || dtype == kFloat32;
+  const uintptr_t places = reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(update) |
+                           reinterpret_cast<uintptr_t>(gain) | reinterpret_cast<uintptr_t>(bias) |
+                           reinterpret_cast<uintptr_t>(out);
+  if (float_terms && hidden % 4 == 0 && hidden <= 16 * 1024 && (places & 15) == 0 && partial_stride % 4 == 0) {
+    // 16-byte pieces: one, two or four a thread
+    int threads = 32;
+    while (threads * kLayerPieces < hidden / 4 && threads < 1024) threads <<= 1;
+    const int splits = update == nullptr ? 0 : (partial_splits > 0 ? partial_splits : 1);
+    DISPATCH_DTYPE(dtype, "add_layernorm", {
+      CIE_LAUNCH("add_layernorm", add_layernorm_x4_kernel<T>, dim3(count), dim3(threads), 0, (cudaStream_t)stream,
+                 residual, (const float*)update, splits, (size_t)partial_stride, update_scale, gain, bias, (T*)out,
+                 rows, hidden, eps);
+    })
+    return 0;
+  }
   DISPATCH_DTYPE(dtype, "add_layernorm", {
     CIE_LAUNCH("add_layernorm", add_layernorm_kernel<T>, dim3(count), dim3(threads_for(hidden / 4)), 0,
                (cudaStream_t)stream, residual, update, partial_splits, (size_t)partial_stride, update_scale,

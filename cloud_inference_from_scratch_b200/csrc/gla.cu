@@ -16,9 +16,10 @@
 //     o_i = (q_i * exp(b_i))^T S_0 + sum_(j<=i) (sum_d q_i[d] k_j[d] exp(b_i[d] - b_j[d])) v_j
 //     S_n = diag(exp(b_n)) S_0 + sum_j (k_j * exp(b_n - b_j)) v_j^T
 //
-// in which no exponent is above zero: (1) per (chunk, head) the sum over j and b_n; (2) per (request, head) a
-// walk over the request's chunks that leaves the state BEFORE each chunk in the sum's place and the last state
-// in the slot; (3) per (chunk, head) the outputs.  Chunks come as a work list made on the host from the step's
+// in which no exponent is above zero: (0) per (chunk, head) the sums b_i, left in the place of the decay logits;
+// (1) per (chunk, head) the sum over j and exp(b_n); (2) per (request, head) a walk over the request's chunks
+// that leaves the state BEFORE each chunk in the sum's place and the last state in the slot; (3) per (chunk,
+// head) the outputs.  Chunks come as a work list made on the host from the step's
 // portion lengths (first token row and token count of each chunk; where every request's chunks start).
 //
 // A request's result depends on its own tokens and state only: the batch and the slot change nothing, the cut
@@ -139,27 +140,35 @@ __device__ __forceinline__ void stage_rows(float* __restrict__ dst, int ld, cons
   }
 }
 
-// b_s[j * ld + d] = sum_(s<=j) log(alpha_s[d]) for the chunk's tokens j < n: every token's logarithm first, then a
-// thread a channel adds them up in token order (two barriers inside).
-__device__ __forceinline__ void stage_decay_sums(float* __restrict__ b_s, int ld, const GlaRows& in, int row0, int n,
-                                                 int head, int dim) {
-  for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
-    const int j = e / dim, d = e % dim;
-    b_s[j * ld + d] = log_decay(in.z[(size_t)(row0 + j) * in.z_stride + head * dim + d] + in.z_bias[head * dim + d],
-                                in.inv_tau);
-  }
-  __syncthreads();
+// (0) z[row0 + j][head][d] <- b_j[d] = sum_(s<=j) log(alpha_s[d]) for the chunk's tokens j < n, in place: a thread a
+// channel adds the logarithms up in token order.  Both kernels that follow read the sums from there.
+__global__ void gla_decay_sums_kernel(float* __restrict__ z, int z_stride, const float* __restrict__ z_bias,
+                                      float inv_tau, const int* __restrict__ chunk_row,
+                                      const int* __restrict__ chunk_count, int dim) {
+  pdl_wait();
+  pdl_trigger();
+  const int chunk = blockIdx.x, head = blockIdx.y;
+  const int row0 = chunk_row[chunk], n = chunk_count[chunk];
   for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    float* cell = z + (size_t)row0 * z_stride + head * dim + d;
+    const float bias = z_bias[head * dim + d];
     float sum = 0.f;
-    for (int j = 0; j < n; ++j) {
-      sum += b_s[j * ld + d];
-      b_s[j * ld + d] = sum;
+    for (int j0 = 0; j0 < n; j0 += 8) {        // eight loads in flight, then their logarithms in token order
+      float y[8];
+#pragma unroll
+      for (int x = 0; x < 8; ++x) y[x] = j0 + x < n ? cell[(size_t)(j0 + x) * z_stride] : 0.f;
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        if (j0 + x < n) {
+          sum += log_decay(y[x] + bias, inv_tau);
+          cell[(size_t)(j0 + x) * z_stride] = sum;
+        }
+      }
     }
   }
-  __syncthreads();
 }
 
-// (1) chunk_state[chunk][head] = sum_j (k_j * exp(b_n - b_j)) v_j^T; chunk_decay[chunk][head][d] = b_n[d].
+// (1) chunk_state[chunk][head] = sum_j (k_j * exp(b_n - b_j)) v_j^T; chunk_decay[chunk][head][d] = exp(b_n[d]).
 __global__ void __launch_bounds__(kScanWarps * 32)
 gla_chunk_state_kernel(GlaRows in, float* __restrict__ chunk_state, float* __restrict__ chunk_decay,
                        const int* __restrict__ chunk_row, const int* __restrict__ chunk_count, int heads, int dim,
@@ -167,20 +176,19 @@ gla_chunk_state_kernel(GlaRows in, float* __restrict__ chunk_state, float* __res
   extern __shared__ __align__(16) float smem[];
   float* k_s = smem;                          // [kChunk][dim], times exp(b_n - b_j)
   float* v_s = k_s + kChunk * dim;            // [kChunk][vdim]
-  float* b_s = v_s + kChunk * vdim;           // [kChunk][dim]
   pdl_wait();
   pdl_trigger();
   const int chunk = blockIdx.x, head = blockIdx.y;
   const int row0 = chunk_row[chunk], n = chunk_count[chunk];
-  stage_rows(k_s, dim, in.proj, in.proj_stride, row0, n, in.k_off + head * dim, dim, 1.f);
   stage_rows(v_s, vdim, in.proj, in.proj_stride, row0, n, in.v_off + head * vdim, vdim, 1.f);
-  stage_decay_sums(b_s, dim, in, row0, n, head, dim);
+  const float* b_last = in.z + (size_t)(row0 + n - 1) * in.z_stride + head * dim;
   for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
     const int j = e / dim, d = e % dim;
-    k_s[e] *= expf(b_s[(n - 1) * dim + d] - b_s[j * dim + d]);
+    const float b = in.z[(size_t)(row0 + j) * in.z_stride + head * dim + d];
+    k_s[e] = in.proj[(size_t)(row0 + j) * in.proj_stride + in.k_off + head * dim + d] * expf(b_last[d] - b);
   }
   for (int d = threadIdx.x; d < dim; d += blockDim.x)
-    chunk_decay[((size_t)chunk * heads + head) * dim + d] = b_s[(n - 1) * dim + d];
+    chunk_decay[((size_t)chunk * heads + head) * dim + d] = expf(b_last[d]);
   __syncthreads();
   // a warp owns kChunkRows state rows that follow each other, a lane the value columns lane, lane + 32, ...
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -248,7 +256,7 @@ __global__ void gla_chunk_prefix_kernel(float* __restrict__ chunk_state, const f
     for (int x = 0; x < kBatch; ++x) {
       const bool in = chunk + x < last;
       gained[x] = in ? u[x * stride] : 0.f;
-      power[x] = in ? expf(b[x * decay_stride]) : 1.f;
+      power[x] = in ? b[x * decay_stride] : 1.f;
     }
 #pragma unroll
     for (int x = 0; x < kBatch; ++x) {
@@ -280,7 +288,8 @@ gla_chunk_output_kernel(GlaRows in, float* __restrict__ out, int out_stride, con
   stage_rows(q_s, dim, in.proj, in.proj_stride, row0, n, in.q_off + head * dim, dim, in.q_scale);
   stage_rows(k_s, ld, in.proj, in.proj_stride, row0, n, in.k_off + head * dim, dim, 1.f);
   stage_rows(v_s, vdim, in.proj, in.proj_stride, row0, n, in.v_off + head * vdim, vdim, 1.f);
-  stage_decay_sums(b_s, ld, in, row0, n, head, dim);
+  stage_rows(b_s, ld, in.z, in.z_stride, row0, n, head * dim, dim, 1.f);
+  __syncthreads();
   // a[i][j] = sum_d q_i[d] k_j[d] exp(b_i[d] - b_j[d]) for j <= i: lanes run over j
   for (int e = threadIdx.x; e < n * kChunk; e += blockDim.x) {
     const int i = e / kChunk, j = e % kChunk;
@@ -394,7 +403,8 @@ extern "C" int cie_gla_scan(const float* proj, int proj_stride, int q_off, int k
 }
 
 // The chunked form.  chunk_state: float32 scratch [chunks][heads][dim][vdim]; chunk_decay: [chunks][heads][dim].
-extern "C" int cie_gla_chunked(const float* proj, int proj_stride, int q_off, int k_off, int v_off, const float* z,
+// z is overwritten (with the running sums of the decays' logarithms inside every chunk).
+extern "C" int cie_gla_chunked(const float* proj, int proj_stride, int q_off, int k_off, int v_off, float* z,
                                int z_stride, const float* z_bias, float inv_tau, float q_scale, float* out,
                                int out_stride, float* state, float* chunk_state, float* chunk_decay,
                                const int* chunk_row, const int* chunk_count, const int* request_chunk_start,
@@ -406,7 +416,7 @@ extern "C" int cie_gla_chunked(const float* proj, int proj_stride, int q_off, in
   if (dim > kChunkDim || vdim > kChunkDim)
     CIE_FAIL("gla_chunked: key / value sizes %d / %d are above %d", dim, vdim, kChunkDim);
   cudaStream_t s = (cudaStream_t)stream;
-  const size_t smem1 = (size_t)kChunk * (2 * dim + vdim) * sizeof(float);
+  const size_t smem1 = (size_t)kChunk * (dim + vdim) * sizeof(float);
   const size_t smem3 = (size_t)kChunk * (dim + vdim + 2 * (dim + 1) + kChunk) * sizeof(float);
   static bool raised = false;
   if (!raised) {
@@ -417,6 +427,10 @@ extern "C" int cie_gla_chunked(const float* proj, int proj_stride, int q_off, in
   }
   dim3 grid(chunks, heads), block(kScanWarps * 32);
   dim3 grid2(requests, heads, (dim * vdim + 255) / 256);
+  int sum_threads = 32;
+  while (sum_threads < dim) sum_threads <<= 1;
+  CIE_LAUNCH("gla_decay_sums", gla_decay_sums_kernel, grid, dim3(sum_threads), 0, s, z, z_stride, z_bias, inv_tau,
+             chunk_row, chunk_count, dim);
   CIE_LAUNCH("gla_chunk_state", gla_chunk_state_kernel, grid, block, smem1, s, in, chunk_state, chunk_decay, chunk_row,
              chunk_count, heads, dim, vdim);
   CIE_LAUNCH("gla_chunk_prefix", gla_chunk_prefix_kernel, grid2, dim3(256), 0, s, chunk_state,

@@ -791,7 +791,8 @@ class Ops:
         """Gated linear attention over every request's new tokens from the state in its slot (``state``: float32
         [slots, heads, dim, vdim]): ``S <- diag(alpha) S + k v^T``, ``o = S^T (q * q_scale)`` with
         ``alpha = sigmoid(z + z_bias)^(1 / tau)`` per head and key channel.  ``proj`` is float32 [T, *] with q, k
-        and v at the columns ``offsets``; ``z`` float32 [T, heads * dim]; ``out`` float32 [T, heads * vdim].  With
+        and v at the columns ``offsets``; ``z`` float32 [T, heads * dim] (the chunked form overwrites it);
+        ``out`` float32 [T, heads * vdim].  With
         ``plan`` (chunk lists of a step with prompt portions) and sizes the chunked kernels take, the recurrence
         runs in chunks; else token by token."""
         self._flush()
@@ -810,7 +811,7 @@ class Ops:
             sums = self.scratch(f"gla.chunks.{heads}x{dim}x{vdim}", chunks * heads * dim * vdim,
                                 reserve=most * heads * dim * vdim)
             decays = self.scratch(f"gla.decays.{heads}x{dim}", chunks * heads * dim, reserve=most * heads * dim)
-            self.launches += 3
+            self.launches += 4
             self._gla_chunked(*head, _ptr(sums), _ptr(decays), _ptr(plan["chunk_row"]), _ptr(plan["chunk_count"]),
                               _ptr(plan["request_chunk_start"]), _ptr(ctx.slots), _ptr(ctx.request_active), chunks,
                               ctx.num_requests, heads, dim, vdim, state.shape[0], _ptr(self.error_word), self.stream)

