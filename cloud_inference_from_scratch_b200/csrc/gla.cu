@@ -182,10 +182,25 @@ gla_chunk_state_kernel(GlaRows in, float* __restrict__ chunk_state, float* __res
   const int row0 = chunk_row[chunk], n = chunk_count[chunk];
   stage_rows(v_s, vdim, in.proj, in.proj_stride, row0, n, in.v_off + head * vdim, vdim, 1.f);
   const float* b_last = in.z + (size_t)(row0 + n - 1) * in.z_stride + head * dim;
-  for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
-    const int j = e / dim, d = e % dim;
-    const float b = in.z[(size_t)(row0 + j) * in.z_stride + head * dim + d];
-    k_s[e] = in.proj[(size_t)(row0 + j) * in.proj_stride + in.k_off + head * dim + d] * expf(b_last[d] - b);
+  const int k_col = in.k_off + head * dim;
+  if (dim % 4 == 0 && k_col % 4 == 0 && in.proj_stride % 4 == 0 && in.z_stride % 4 == 0 &&
+      ((reinterpret_cast<uintptr_t>(in.proj) | reinterpret_cast<uintptr_t>(in.z)) & 15) == 0) {
+    // 16-byte pieces of the key rows and of the sums (one index division a piece)
+    const int pieces = dim / 4;
+    for (int e = threadIdx.x; e < n * pieces; e += blockDim.x) {
+      const int j = e / pieces, d = (e % pieces) * 4;
+      const float4 b = *reinterpret_cast<const float4*>(in.z + (size_t)(row0 + j) * in.z_stride + head * dim + d);
+      const float4 last = *reinterpret_cast<const float4*>(b_last + d);
+      float4 k = *reinterpret_cast<const float4*>(in.proj + (size_t)(row0 + j) * in.proj_stride + k_col + d);
+      k.x *= expf(last.x - b.x); k.y *= expf(last.y - b.y); k.z *= expf(last.z - b.z); k.w *= expf(last.w - b.w);
+      *reinterpret_cast<float4*>(k_s + j * dim + d) = k;
+    }
+  } else {
+    for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
+      const int j = e / dim, d = e % dim;
+      const float b = in.z[(size_t)(row0 + j) * in.z_stride + head * dim + d];
+      k_s[e] = in.proj[(size_t)(row0 + j) * in.proj_stride + k_col + d] * expf(b_last[d] - b);
+    }
   }
   for (int d = threadIdx.x; d < dim; d += blockDim.x)
     chunk_decay[((size_t)chunk * heads + head) * dim + d] = expf(b_last[d]);
@@ -288,26 +303,35 @@ gla_chunk_output_kernel(GlaRows in, float* __restrict__ out, int out_stride, con
   stage_rows(q_s, dim, in.proj, in.proj_stride, row0, n, in.q_off + head * dim, dim, in.q_scale);
   stage_rows(k_s, ld, in.proj, in.proj_stride, row0, n, in.k_off + head * dim, dim, 1.f);
   stage_rows(v_s, vdim, in.proj, in.proj_stride, row0, n, in.v_off + head * vdim, vdim, 1.f);
-  stage_rows(b_s, ld, in.z, in.z_stride, row0, n, head * dim, dim, 1.f);
+  // the sums in units of log 2: every exponential below is one exp2
+  stage_rows(b_s, ld, in.z, in.z_stride, row0, n, head * dim, dim, 1.4426950408889634f);
   __syncthreads();
-  // a[i][j] = sum_d q_i[d] k_j[d] exp(b_i[d] - b_j[d]) for j <= i: lanes run over j
-  for (int e = threadIdx.x; e < n * kChunk; e += blockDim.x) {
-    const int i = e / kChunk, j = e % kChunk;
-    float dot = 0.f;
-    if (j <= i) {
-      const float* qi = q_s + i * dim;
-      const float* bi = b_s + i * ld;
-      const float* kj = k_s + j * ld;
-      const float* bj = b_s + j * ld;
-      for (int x = 0; x < dim; ++x) dot = fmaf(qi[x] * kj[x], expf(bi[x] - bj[x]), dot);
+  // a[i][j] = sum_d q_i[d] k_j[d] exp(b_i[d] - b_j[d]) for j <= i.  Only those pairs are dealt out: pair p is
+  // (i, j) with p = i (i + 1) / 2 + j, so neighbouring lanes mostly share i and walk neighbouring rows j
+  const int pairs = n * (n + 1) / 2;
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+    int i = (int)((sqrtf(8.f * (float)p + 1.f) - 1.f) * 0.5f);
+    while (i * (i + 1) / 2 > p) --i;
+    while ((i + 1) * (i + 2) / 2 <= p) ++i;
+    const int j = p - i * (i + 1) / 2;
+    const float* qi = q_s + i * dim;
+    const float* bi = b_s + i * ld;
+    const float* kj = k_s + j * ld;
+    const float* bj = b_s + j * ld;
+    float dot = 0.f, dot2 = 0.f;       // two chains
+    int x = 0;
+    for (; x + 2 <= dim; x += 2) {
+      dot = fmaf(qi[x] * kj[x], exp2f(bi[x] - bj[x]), dot);
+      dot2 = fmaf(qi[x + 1] * kj[x + 1], exp2f(bi[x + 1] - bj[x + 1]), dot2);
     }
-    a_s[e] = dot;
+    if (x < dim) dot = fmaf(qi[x] * kj[x], exp2f(bi[x] - bj[x]), dot);
+    a_s[i * kChunk + j] = dot + dot2;
   }
   __syncthreads();
   // what the carried state is read with: q_i * exp(b_i)
   for (int e = threadIdx.x; e < n * dim; e += blockDim.x) {
     const int i = e / dim, x = e % dim;
-    q_s[e] *= expf(b_s[i * ld + x]);
+    q_s[e] *= exp2f(b_s[i * ld + x]);
   }
   __syncthreads();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
