@@ -654,7 +654,7 @@ def _bilipel(width, layers, loop, heads, kv_heads, dim, rot_dim, kv_rank, window
              expert_ff, vocab=32000) -> dict:
     """``layers``: a string of A (softmax attention with a sink, with a dense feed-forward), L (windowed latent
     attention, routed experts) and G (gated linear attention, routed experts); ``loop``: (start, stop, times)."""
-    rot = dict(base=250000.0, dims=dim // 2, scaling=dict(factor=8.0, original=1024, fast=32.0, slow=1.0))
+    rot = dict(base=500000.0, dims=dim // 2, scaling=dict(factor=4.0, original=2048, fast=16.0, slow=2.0))
     moe = dict(kind="moe", expert=dict(ff=expert_ff), router=dict(experts=experts, top=top))
     kinds = {
         "A": dict(type="attention", mixer=dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5, rot=rot),
@@ -662,9 +662,9 @@ def _bilipel(width, layers, loop, heads, kv_heads, dim, rot_dim, kv_rank, window
         "L": dict(type="latent_attention",
                   mixer=dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=dim, kv_rank=kv_rank, scale=(dim + rot_dim) ** -0.5,
                              rot=dict(base=10000.0, dims=rot_dim), mask=dict(size=window)), mlp=moe),
-        "G": dict(type="gla", mixer=dict(heads=gla_heads, dim=dim, vdim=dim, tau=16.0, decay_rank=64), mlp=moe),
+        "G": dict(type="gla", mixer=dict(heads=gla_heads, dim=dim, vdim=dim, tau=8.0, decay_rank=64), mlp=moe),
     }
-    raw = dict(architecture="Bilipel", vocab=vocab, width=width, norm=dict(eps=1e-5), residual_mult=0.3,
+    raw = dict(architecture="Bilipel", vocab=vocab, width=width, norm=dict(eps=1e-6), residual_mult=0.5,
                layers=[kinds[letter] for letter in layers])
     if loop is not None:
         raw["loop"] = dict(start=loop[0], stop=loop[1], times=loop[2])

@@ -9,7 +9,7 @@
 // Keys are visited in blocks of 32 counted from the first visible key, so the result for a
 // token depends only on its request's keys, not on the batch, the cut or the pages used.
 //
-// Two generalisations (cie_attention_generic_ex): value heads of a size of their own (`vdim`), and
+// Two generalisations: value heads of a size of their own (`vdim`), and
 // a logarithmic distance penalty per query head, s = (q.k) * scale - r1[h] * log(1 + r2[h] * (p - j))
 // for a key at position j (r1 == nullptr: none).
 //
@@ -429,40 +429,4 @@ extern "C" int cie_attention_generic_sink(const void* q, int q_stride, void* out
     CIE_FAIL("attention_generic: unknown element type code %d", dtype);
   }
   return 0;
-}
-
-extern "C" int cie_attention_generic_split(const void* q, int q_stride, void* out, int out_stride,
-                                           const void* k_pool, const void* v_pool, const int* positions,
-                                           const int* request_of_token, const int* table, int table_width,
-                                           int num_pages, int tokens, int q_heads, int kv_heads, int dim,
-                                           int vdim, int page_size, float scale, int window,
-                                           const float* r1, const float* r2, int splits, float* shares,
-                                           int* tickets, int keep_first, int dtype, int* err, void* stream) {
-  return cie_attention_generic_sink(q, q_stride, out, out_stride, k_pool, v_pool, positions, request_of_token,
-                                    table, table_width, num_pages, tokens, q_heads, kv_heads, dim, vdim,
-                                    page_size, scale, window, r1, r2, splits, shares, tickets, keep_first, nullptr,
-                                    dtype, err, stream);
-}
-
-extern "C" int cie_attention_generic_ex(const void* q, int q_stride, void* out, int out_stride,
-                                        const void* k_pool, const void* v_pool, const int* positions,
-                                        const int* request_of_token, const int* table, int table_width,
-                                        int num_pages, int tokens, int q_heads, int kv_heads, int dim,
-                                        int vdim, int page_size, float scale, int window,
-                                        const float* r1, const float* r2, int dtype, int* err,
-                                        void* stream) {
-  return cie_attention_generic_split(q, q_stride, out, out_stride, k_pool, v_pool, positions, request_of_token,
-                                     table, table_width, num_pages, tokens, q_heads, kv_heads, dim, vdim,
-                                     page_size, scale, window, r1, r2, 1, nullptr, nullptr, 0, dtype, err, stream);
-}
-
-extern "C" int cie_attention_generic(const void* q, int q_stride, void* out, int out_stride,
-                                     const void* k_pool, const void* v_pool, const int* positions,
-                                     const int* request_of_token, const int* table, int table_width,
-                                     int num_pages, int tokens, int q_heads, int kv_heads, int dim,
-                                     int page_size, float scale, int window, int dtype, int* err,
-                                     void* stream) {
-  return cie_attention_generic_ex(q, q_stride, out, out_stride, k_pool, v_pool, positions, request_of_token,
-                                  table, table_width, num_pages, tokens, q_heads, kv_heads, dim, dim,
-                                  page_size, scale, window, nullptr, nullptr, dtype, err, stream);
 }

@@ -107,18 +107,6 @@ class Ops:
         gs = _Lib(load_library("gemm_simt.cu"))
         self._gemm_simt = gs.function("cie_gemm_simt", [v, v, v, v, i, i, i, i, i, i, v])
         ag = _Lib(load_library("attention_generic.cu"))
-        self._attention_generic = ag.function(
-            "cie_attention_generic",
-            [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, f, i, i, v, v],
-        )
-        self._attention_generic_ex = ag.function(
-            "cie_attention_generic_ex",
-            [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, i, f, i, v, v, i, v, v],
-        )
-        self._attention_generic_split = ag.function(
-            "cie_attention_generic_split",
-            [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, i, f, i, v, v, i, v, v, i, i, v, v],
-        )
         self._attention_generic_sink = ag.function(
             "cie_attention_generic_sink",
             [v, i, v, i, v, v, v, v, v, i, i, i, i, i, i, i, i, f, i, v, v, i, v, v, i, v, i, v, v],
